@@ -1,0 +1,165 @@
+/*
+ * Host surface of the engine: the reference's own model/cache structs and entry points
+ * (abhisheknair10/LLM.cu src/llama3/llama3.cuh, src/safetensor/safetensor.cuh,
+ * src/inference/inference.cuh, src/tokenizer/tokenizer.cuh), re-implemented on top of the
+ * sm_100a kernels of llm_b200.h.  A driver written against the reference (src/main.cu:61-126)
+ * compiles against this header and links libllm_b200.so instead of the reference's objects.
+ *
+ * Differences a caller can see:
+ *  - dimensions are no longer literals: they are derived from the tensor shapes at to_cuda()
+ *    and can be completed with llama3_set_config() (head_dim, rope_theta, eps, max_seq);
+ *  - inference() keeps a per-layer KV cache, so a call costs one token, not the whole
+ *    sequence (the reference recomputes every row each call, inference.cu:153-188);
+ *  - inference() returns the greedy argmax computed on the device (the reference samples with
+ *    temperature/top-p on the host, inference.cu:1030-1039); the FP16 logits are still left in
+ *    Cache->h_token_probdist / d_token_probdist (inference.cu:1021-1025);
+ *  - every entry point has an int-status twin (llama3_*): the reference-named void functions
+ *    print and exit(1) as the reference does, the twins return an LLMB_ERR_* code.
+ * All functions have C linkage.
+ */
+#ifndef LLM_B200_LLAMA3_H
+#define LLM_B200_LLAMA3_H
+
+#include <stdint.h>
+
+#include "llm_b200.h"
+
+#if defined(__CUDACC__) || defined(LLMB_HAVE_CUDA_FP16)
+#include <cuda_fp16.h>
+typedef __half llmb_half;
+#else
+typedef uint16_t llmb_half;
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* llama3.cuh:10-23.  The first ten fields are the reference's, in its order. */
+typedef struct {
+    /* host */
+    int *ndim;
+    int *mem_len;
+    int *shape;
+    uint16_t *bf16_tensor; /* payload as read from the file; freed by to_cuda */
+    /* device */
+    int *d_ndim;
+    int *d_mem_len;
+    int *d_shape;
+    uint16_t *d_bf16_tensor;
+    llmb_half *d_fp16_tensor;
+    /* additions */
+    int file_dtype;     /* 0 = BF16 (converted at load), 1 = F16 (passed through) */
+    int device_is_view; /* d_fp16_tensor points into a fused buffer owned by another tensor */
+    int loaded;
+} Tensor;
+
+/* llama3.cuh:28-39 */
+typedef struct {
+    int layernum;
+    Tensor *input_layernorm;
+    Tensor *mlp_down_proj;
+    Tensor *mlp_gate_proj;
+    Tensor *mlp_up_proj;
+    Tensor *post_attention_layernorm;
+    Tensor *self_attn_k_proj;
+    Tensor *self_attn_o_proj;
+    Tensor *self_attn_q_proj;
+    Tensor *self_attn_v_proj;
+} Llama3Layer;
+
+/* The reference has no config struct: every dimension is a literal in inference.cu. */
+typedef struct {
+    int d_model;    /* 4096  (inference.cu:212) */
+    int n_q_heads;  /* 32    (inference.cu:700) */
+    int n_kv_heads; /* 8     (inference.cu:752: group of 4) */
+    int head_dim;   /* 128   (inference.cu:673, 710) */
+    int ffn;        /* 14336 */
+    int vocab;      /* 128256 (inference.cu:24) */
+    int max_seq;    /* 2048  (inference.cu:122-124): KV-cache rows per layer */
+    float rope_theta; /* 500000 (inference.cu:673) */
+    double eps;       /* 1e-5, a double literal in the reference (inference.cu:351) */
+} Llama3Config;
+
+/* llama3.cuh:44-50 plus the additions after n_layers. */
+typedef struct {
+    Tensor *embed_tokens;
+    Tensor *lm_head;
+    Tensor *norm;
+    Llama3Layer **layers;
+    int n_layers;
+    /* additions */
+    Llama3Config config;
+    int config_ready; /* set by to_cuda once shapes are known */
+    int tp_rank, tp_size;
+    void *priv; /* fused device buffers */
+} Llama3;
+
+/* inference.cuh:19-34.  Same field names; K and V now hold the per-layer KV cache
+ * ([n_layers * max_seq][n_kv_heads * head_dim], K stored post-RoPE) instead of one layer's
+ * scratch, and the N x N score buffer is never allocated. */
+typedef struct {
+    Tensor *PN_X; /* unused by the fused kernels (residual add happens in the epilogues); kept NULL */
+    Tensor *Q;    /* [1][n_q_heads * head_dim] query row of the current token */
+    Tensor *K;
+    Tensor *V;
+    float *d_attention_score_cache;          /* always NULL */
+    llmb_half *d_feedforward_cache_upgate;   /* [ffn] SwiGLU output of the current token */
+    llmb_half *d_token_probdist;             /* [vocab] FP16 logits on the device */
+    llmb_half *h_token_probdist;             /* [vocab] FP16 logits on the host (pinned) */
+    float *f_token_probdist;                 /* [vocab] host scratch, kept for callers that sample */
+    /* additions */
+    void *priv;
+} CudaCache;
+
+/* ---- reference-named entry points ------------------------------------------------------- */
+Llama3 *init_llama3(int n_layers);                                      /* llama3.cuh:58 */
+void free_llama3(Llama3 *llama3);                                       /* llama3.cuh:68 */
+void _free_tensor(Tensor *tensor);                                      /* llama3.cuh:77 */
+void load_safetensor_weights(Llama3 *llama3_model, const char *filename); /* safetensor.cuh:26 */
+void to_cuda(Llama3 *llama3);                                           /* llama3.cuh:86 */
+CudaCache *init_cache(Llama3 *llama3_model);                            /* inference.cuh:447 */
+int *tokens_to_cuda(int *tokens, int embed_size, Tensor *token_tensor); /* tokenizer.cuh:66 */
+/* inference.cuh:71.  h_tokens[0] = count + 1, ids in h_tokens[1..count] (tokenizer.cu:143-152).
+ * Processes the tokens not yet in the KV cache (all of them on the first call, one per call
+ * afterwards), returns the greedy next token id, or a negative LLMB_ERR_* code.  X and
+ * d_tokens are the buffers tokens_to_cuda() returned. */
+int inference(Llama3 *llama3_model, Tensor *X, int *d_tokens, int *h_tokens, CudaCache *Cache);
+
+/* ---- status-returning twins and additions ----------------------------------------------- */
+int llama3_set_config(Llama3 *m, const Llama3Config *cfg); /* fields <= 0 keep their default */
+int llama3_set_tp(Llama3 *m, int tp_rank, int tp_size);
+int llama3_load_safetensors(Llama3 *m, const char *filename);
+int llama3_to_cuda(Llama3 *m);
+/* Random-init model written directly in device memory with the seeded generator of
+ * llm_b200_synth.h (std 0.02, norm gains 1.0), BF16 then converted by the load-time kernel
+ * (bf16 != 0) or FP16 drawn directly (bf16 == 0).  cfg must be complete. */
+int llama3_synth_weights(Llama3 *m, const Llama3Config *cfg, uint64_t seed, int bf16);
+CudaCache *llama3_init_cache(Llama3 *m, int *status_out);
+void free_cache(CudaCache *cache);
+/* Forget the cached sequence (next inference() call starts a new one). */
+int cache_reset(CudaCache *cache);
+/* Switches: use_graph (capture each decode step into a CUDA graph, default 1), use_pdl
+ * (programmatic dependent launch between kernels, default 1), copy_logits (device->host copy
+ * of the logits on every call, default 1). Negative value = leave unchanged. */
+int cache_set_options(CudaCache *cache, int use_graph, int use_pdl, int copy_logits);
+/* When enabled, every decode step also copies the residual stream after the embedding and
+ * after each layer into an [n_layers + 1][d_model] FP16 device buffer (disables the graph). */
+int cache_enable_hidden_dump(CudaCache *cache, int enable);
+int cache_read_hidden(CudaCache *cache, uint16_t *h_out /* [n_layers+1][d_model] */);
+/* Device-resident greedy generation: prefill `n_prompt` ids, then generate `n_new` tokens with
+ * the sampled token fed back on the device (no host round trip per token).
+ * out_tokens[n_new]; prefill_ms / decode_ms (optional) are CUDA-event times. */
+int inference_greedy(Llama3 *m, CudaCache *cache, const int *prompt, int n_prompt, int n_new, int *out_tokens,
+                     float *prefill_ms, float *decode_ms);
+/* Continues a greedy run for n_steps more tokens from the state inference_greedy() (or a previous
+ * inference_continue) left: the last sampled token is fed back on the device.  out_tokens[n_steps];
+ * ms (optional) is the CUDA-event time of the n_steps steps. */
+int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int *out_tokens, float *ms);
+/* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
+long long cache_kernel_launches(const CudaCache *cache);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLM_B200_LLAMA3_H */

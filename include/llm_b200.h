@@ -1,0 +1,156 @@
+/*
+ * llm_b200: C-ABI of the sm_100a kernels behind the LLaMA3 per-token forward loop.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream and returns an int status (0 = ok).  No entry point
+ * allocates device memory unless its comment says so.  FP16 and BF16 data travel as
+ * uint16_t bit patterns so that the header needs no CUDA include.
+ *
+ * Each declaration cites the part of the reference engine (abhisheknair10/LLM.cu, paths
+ * relative to its root) that it replaces.
+ */
+#ifndef LLM_B200_H
+#define LLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *llmb_stream_t; /* a cudaStream_t */
+
+enum {
+    LLMB_OK = 0,
+    LLMB_ERR_INVALID = 1,     /* bad argument (null pointer, unsupported shape, misalignment) */
+    LLMB_ERR_CUDA = 2,        /* a CUDA runtime call failed; see llmb_last_error() */
+    LLMB_ERR_TIMEOUT = 3,     /* a bounded device-side wait ran out (llmb_device_status) */
+    LLMB_ERR_UNSUPPORTED = 4, /* valid request that this build has no kernel for */
+    LLMB_ERR_IO = 5,          /* file missing, truncated or malformed */
+    LLMB_ERR_NOMEM = 6
+};
+
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char *llmb_last_error(void);
+
+/* Reads and clears the per-device status word kernels set when a bounded wait gives up.
+ * Synchronises the device. */
+int llmb_device_status(int *status_out);
+
+/* Library build identification: "sm_100a" and the kernels compiled in. */
+const char *llmb_build_info(void);
+
+/* ------------------------------------------------------------------------------------ */
+/* Load-time conversion.  Replaces _kernel_bf16_to_fp16 (src/llama3/llama3.cu:240-254):  */
+/* fp16 = RN(fp32(bf16 << 16)).  128-bit loads and stores; n elements.                   */
+/* ------------------------------------------------------------------------------------ */
+int llmb_bf16_to_fp16(const uint16_t *d_bf16, uint16_t *d_fp16, size_t n, llmb_stream_t stream);
+
+/* Seeded synthetic BF16/FP16 weights written directly in device memory
+ * (include/llm_b200_synth.h defines the stream).  Benchmark and test support: the reference
+ * ships no weights (model_weights/README.md). */
+int llmb_synth_bf16(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, uint64_t first, uint64_t n,
+                    llmb_stream_t stream);
+int llmb_synth_fp16(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, uint64_t first, uint64_t n,
+                    llmb_stream_t stream);
+int llmb_fill_u16(uint16_t *d_out, uint16_t value, uint64_t n, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Step prologue.  Replaces tokens_to_embeddings / kernel_tokens_to_embeddings           */
+/* (src/inference/inference.cu:196-223) for the rows processed in this call, and          */
+/* precomputes the RoPE angles kernel_rope_scaling (inference.cu:640-695) would derive     */
+/* per element: cs[row][i] = (cosf, sinf)(pos * theta^(-2i/head_dim)), FP32.               */
+/*   tokens   : device int32 ids: row r uses tokens[r], or tokens[pos[r]] when              */
+/*              tokens_by_pos != 0 (tokens is then the sequence history, so a captured      */
+/*              step can be replayed while only pos advances)                              */
+/*   pos      : device int32 position of each row                                         */
+/*   x        : out, [n_rows][d_model] FP16                                               */
+/*   rope_cs  : out, [n_rows][head_dim/2][2] FP32                                         */
+/* ------------------------------------------------------------------------------------ */
+int llmb_embed_rope(const uint16_t *d_embed, const int32_t *d_tokens, const int32_t *d_pos, int n_rows, int d_model,
+                    int vocab, int head_dim, float rope_theta, uint16_t *d_x, float *d_rope_cs,
+                    int tokens_by_pos, int use_pdl, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Batch-1 projections: y = W x with W [n][k] FP16 row-major (as the checkpoint stores it) */
+/* and FP32 accumulation.  One bandwidth-bound kernel replaces kernel_standard_tiled_gemm  */
+/* at m = 1 (inference.cu:393-449) together with the element-wise kernels around it:       */
+/*                                                                                         */
+/*  prologue LLMB_PRO_RMSNORM  kernel_compute_rms_norm (inference.cu:293-363): x is the    */
+/*                             residual stream and is normalised on the fly,               */
+/*                             half((x*g)/sqrtf(eps + sum(x^2)/k)), same FP32 summation    */
+/*                             tree as the reference when k/4 is a power of two            */
+/*  epilogue LLMB_EPI_STORE    y[n] = half(acc)                         (inference.cu:445) */
+/*           LLMB_EPI_RESIDUAL y[n] = half(float(half(acc)) + float(y[n]))                 */
+/*                             = GEMM + kernel_add_norm (inference.cu:377-390), in place   */
+/*           LLMB_EPI_ROPE_KV  rows [0,n_q) -> RoPE -> q; rows [n_q,n_q+n_kv) -> RoPE ->   */
+/*                             K cache row `pos`; rest -> V cache row `pos`                 */
+/*                             = compute_qkv_tensors + rope_scaling (inference.cu:561-695)  */
+/*           LLMB_EPI_SWIGLU   y[n] = half(SiLU(acc_gate) * acc_up), w = gate, w2 = up      */
+/*                             = kernel_standard_tiled_gemm_ffn_swiglu (inference.cu:455)   */
+/* ------------------------------------------------------------------------------------ */
+enum { LLMB_PRO_NONE = 0, LLMB_PRO_RMSNORM = 1 };
+enum { LLMB_EPI_STORE = 0, LLMB_EPI_RESIDUAL = 1, LLMB_EPI_ROPE_KV = 2, LLMB_EPI_SWIGLU = 3 };
+
+typedef struct {
+    const uint16_t *w;     /* [n][k] FP16 */
+    const uint16_t *w2;    /* SWIGLU only: up projection [n][k] */
+    const uint16_t *x;     /* [k] FP16 input row */
+    uint16_t *y;           /* output row (meaning depends on the epilogue), n or n_q elements */
+    int n;                 /* output rows of w (for ROPE_KV: n_q + 2 * n_kv) */
+    int k;                 /* multiple of 8, at most 16384 */
+    int prologue;
+    const uint16_t *gamma; /* RMSNORM: [k] FP16 gain */
+    double eps;            /* RMSNORM: added in double as the reference does (1e-5) */
+    int epilogue;
+    /* ROPE_KV */
+    int n_q;               /* query rows (n_q_heads * head_dim) */
+    int n_kv;              /* key rows = value rows (n_kv_heads * head_dim) */
+    int head_dim;
+    const float *rope_cs;  /* [head_dim/2][2] (cos, sin) of this row's position */
+    uint16_t *k_cache;     /* this layer's and sequence's K rows: [max_pos][n_kv] FP16 */
+    uint16_t *v_cache;
+    const int32_t *pos;    /* device: row index to write in the cache */
+    int max_pos;
+    int use_pdl;           /* launch with programmatic stream serialization */
+} LlmbGemvArgs;
+
+int llmb_gemv_f16(const LlmbGemvArgs *args, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Decode attention over the KV cache for one new token per sequence.  Replaces           */
+/* compute_attention and its three kernels (inference.cu:698-947) for the last row:        */
+/* scores (q.k)/sqrtf(head_dim) in FP32 from FP16, softmax in FP32, P.V in FP32, FP16 out; */
+/* the N x N score matrix is never materialised.  The KV sequence is split across CTAs;    */
+/* partial (max, sum, out) triples go through `scratch` and the last CTA of each KV head   */
+/* merges them.                                                                            */
+/*   q        : [n_q_heads][head_dim] FP16 (post-RoPE)                                     */
+/*   k_cache  : [max_pos][n_kv_heads][head_dim] FP16 (post-RoPE), positions 0..pos valid   */
+/*   out      : [n_q_heads][head_dim] FP16                                                 */
+/*   scratch  : llmb_attn_decode_scratch_bytes() bytes, 256-byte aligned; the first         */
+/*              n_kv_heads int32 counters must be zero before the first call (the kernel    */
+/*              leaves them zero)                                                          */
+/* ------------------------------------------------------------------------------------ */
+size_t llmb_attn_decode_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int n_splits);
+int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, const int32_t *d_pos,
+                     int n_q_heads, int n_kv_heads, int head_dim, int n_splits, int split_len, uint16_t *d_out,
+                     void *d_scratch, int use_pdl, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Greedy sampling on the device: index of the first maximum of n FP16 logits (NaN never   */
+/* wins).  Replaces the host sampler sample_next_token (inference.cu:1030-1161) for greedy */
+/* decoding.  Also advances the step state so a captured step can be replayed without the   */
+/* host: token_out[0] = argmax; if pos_inout != NULL, (*pos_inout)++;                       */
+/* if history != NULL, history[*pos_inout (after increment)] = argmax.                     */
+/* ------------------------------------------------------------------------------------ */
+int llmb_argmax_f16(const uint16_t *d_logits, int n, int32_t *d_token_out, int32_t *d_pos_inout,
+                    int32_t *d_history, int history_len, int use_pdl, llmb_stream_t stream);
+
+/* position += 1 without sampling (prompt rows whose logits nobody reads). */
+int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLM_B200_H */

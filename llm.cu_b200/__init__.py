@@ -1,0 +1,166 @@
+"""ctypes binding of libllm_b200.so: the sm_100a kernels (include/llm_b200.h) and the host
+surface that mirrors the reference engine's entry points (include/llama3.h).
+
+The directory name contains a dot, so load the package by path::
+
+    spec = importlib.util.spec_from_file_location(
+        "llm_cu_b200", "<repo>/llm.cu_b200/__init__.py",
+        submodule_search_locations=["<repo>/llm.cu_b200"])
+
+There is no CPU fallback: importing raises if the shared library has not been built
+(`python llm.cu_b200/build.py`), and every compute call goes to the CUDA library.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libllm_b200.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_IO, ERR_NOMEM = range(7)
+PRO_NONE, PRO_RMSNORM = 0, 1
+EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
+
+# Symbols include/llm_b200.h and include/llama3.h declare; tests check each is exported.
+KERNEL_SYMBOLS = [
+    "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
+    "llmb_synth_fp16", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
+    "llmb_attn_decode", "llmb_argmax_f16", "llmb_advance_pos",
+]
+HOST_SYMBOLS = [
+    "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
+    "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
+    "llama3_to_cuda", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
+    "cache_set_options", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue",
+    "cache_kernel_launches",
+]
+
+
+class LlmbError(RuntimeError):
+    def __init__(self, code, where):
+        self.code = code
+        msg = lib.llmb_last_error().decode("utf-8", "replace") if lib is not None else ""
+        super().__init__("%s failed with status %d%s" % (where, code, (": " + msg) if msg else ""))
+
+
+class TensorStruct(C.Structure):
+    _fields_ = [
+        ("ndim", C.POINTER(C.c_int)), ("mem_len", C.POINTER(C.c_int)), ("shape", C.POINTER(C.c_int)),
+        ("bf16_tensor", C.c_void_p), ("d_ndim", C.c_void_p), ("d_mem_len", C.c_void_p), ("d_shape", C.c_void_p),
+        ("d_bf16_tensor", C.c_void_p), ("d_fp16_tensor", C.c_void_p), ("file_dtype", C.c_int),
+        ("device_is_view", C.c_int), ("loaded", C.c_int),
+    ]
+
+
+class Llama3LayerStruct(C.Structure):
+    _fields_ = [("layernum", C.c_int)] + [
+        (n, C.POINTER(TensorStruct))
+        for n in ("input_layernorm", "mlp_down_proj", "mlp_gate_proj", "mlp_up_proj", "post_attention_layernorm",
+                  "self_attn_k_proj", "self_attn_o_proj", "self_attn_q_proj", "self_attn_v_proj")
+    ]
+
+
+class Llama3Config(C.Structure):
+    _fields_ = [
+        ("d_model", C.c_int), ("n_q_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int),
+        ("ffn", C.c_int), ("vocab", C.c_int), ("max_seq", C.c_int), ("rope_theta", C.c_float), ("eps", C.c_double),
+    ]
+
+
+class Llama3Struct(C.Structure):
+    _fields_ = [
+        ("embed_tokens", C.POINTER(TensorStruct)), ("lm_head", C.POINTER(TensorStruct)),
+        ("norm", C.POINTER(TensorStruct)), ("layers", C.POINTER(C.POINTER(Llama3LayerStruct))),
+        ("n_layers", C.c_int), ("config", Llama3Config), ("config_ready", C.c_int), ("tp_rank", C.c_int),
+        ("tp_size", C.c_int), ("priv", C.c_void_p),
+    ]
+
+
+class CudaCacheStruct(C.Structure):
+    _fields_ = [
+        ("PN_X", C.POINTER(TensorStruct)), ("Q", C.POINTER(TensorStruct)), ("K", C.POINTER(TensorStruct)),
+        ("V", C.POINTER(TensorStruct)), ("d_attention_score_cache", C.c_void_p),
+        ("d_feedforward_cache_upgate", C.c_void_p), ("d_token_probdist", C.c_void_p),
+        ("h_token_probdist", C.c_void_p), ("f_token_probdist", C.c_void_p), ("priv", C.c_void_p),
+    ]
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("w2", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("n", C.c_int), ("k", C.c_int),
+        ("prologue", C.c_int), ("gamma", C.c_void_p), ("eps", C.c_double), ("epilogue", C.c_int), ("n_q", C.c_int),
+        ("n_kv", C.c_int), ("head_dim", C.c_int), ("rope_cs", C.c_void_p), ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p), ("pos", C.c_void_p), ("max_pos", C.c_int), ("use_pdl", C.c_int),
+    ]
+
+
+def _declare(l):
+    vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
+    l.llmb_last_error.restype = C.c_char_p
+    l.llmb_build_info.restype = C.c_char_p
+    l.llmb_device_status.argtypes = [C.POINTER(C.c_int)]
+    l.llmb_bf16_to_fp16.argtypes = [vp, vp, sz, vp]
+    l.llmb_synth_bf16.argtypes = [vp, u64, u64, C.c_float, u64, u64, vp]
+    l.llmb_synth_fp16.argtypes = [vp, u64, u64, C.c_float, u64, u64, vp]
+    l.llmb_fill_u16.argtypes = [vp, C.c_uint16, u64, vp]
+    l.llmb_embed_rope.argtypes = [vp, vp, vp, i32, i32, i32, i32, C.c_float, vp, vp, i32, i32, vp]
+    l.llmb_gemv_f16.argtypes = [C.POINTER(GemvArgs), vp]
+    l.llmb_attn_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
+    l.llmb_attn_decode_scratch_bytes.restype = sz
+    l.llmb_attn_decode.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+    l.llmb_argmax_f16.argtypes = [vp, i32, vp, vp, vp, i32, i32, vp]
+    l.llmb_advance_pos.argtypes = [vp, i32, vp]
+    M, K = C.POINTER(Llama3Struct), C.POINTER(CudaCacheStruct)
+    l.init_llama3.argtypes = [i32]
+    l.init_llama3.restype = M
+    l.free_llama3.argtypes = [M]
+    l.free_llama3.restype = None
+    l._free_tensor.argtypes = [C.POINTER(TensorStruct)]
+    l._free_tensor.restype = None
+    l.load_safetensor_weights.argtypes = [M, C.c_char_p]
+    l.load_safetensor_weights.restype = None
+    l.to_cuda.argtypes = [M]
+    l.to_cuda.restype = None
+    l.init_cache.argtypes = [M]
+    l.init_cache.restype = K
+    l.tokens_to_cuda.argtypes = [C.POINTER(C.c_int), i32, C.POINTER(TensorStruct)]
+    l.tokens_to_cuda.restype = vp
+    l.inference.argtypes = [M, C.POINTER(TensorStruct), vp, C.POINTER(C.c_int), K]
+    l.llama3_set_config.argtypes = [M, C.POINTER(Llama3Config)]
+    l.llama3_set_tp.argtypes = [M, i32, i32]
+    l.llama3_load_safetensors.argtypes = [M, C.c_char_p]
+    l.llama3_to_cuda.argtypes = [M]
+    l.llama3_synth_weights.argtypes = [M, C.POINTER(Llama3Config), u64, i32]
+    l.llama3_init_cache.argtypes = [M, C.POINTER(C.c_int)]
+    l.llama3_init_cache.restype = K
+    l.free_cache.argtypes = [K]
+    l.free_cache.restype = None
+    l.cache_reset.argtypes = [K]
+    l.cache_set_options.argtypes = [K, i32, i32, i32]
+    l.cache_enable_hidden_dump.argtypes = [K, i32]
+    l.cache_read_hidden.argtypes = [K, vp]
+    l.inference_greedy.argtypes = [M, K, C.POINTER(C.c_int), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_float),
+                                   C.POINTER(C.c_float)]
+    l.inference_continue.argtypes = [M, K, i32, C.POINTER(C.c_int), C.POINTER(C.c_float)]
+    l.cache_kernel_launches.argtypes = [K]
+    l.cache_kernel_launches.restype = C.c_longlong
+
+
+lib = None
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "llm.cu_b200: %s is missing. Build it with `python llm.cu_b200/build.py` "
+        "(nvcc, sm_100a). There is no CPU or PyTorch fallback." % LIB_PATH)
+lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+_declare(lib)
+
+
+def check(code, where):
+    if code != OK:
+        raise LlmbError(code, where)
+
+
+from .configs import CONFIGS, ModelConfig  # noqa: E402
+from .engine import Cache, Model  # noqa: E402
+
+__all__ = ["lib", "check", "LlmbError", "Llama3Config", "GemvArgs", "Model", "Cache", "CONFIGS", "ModelConfig",
+           "KERNEL_SYMBOLS", "HOST_SYMBOLS", "LIB_PATH"]

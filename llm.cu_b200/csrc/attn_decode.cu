@@ -1,0 +1,280 @@
+// Decode attention over the KV cache (one query row, grouped-query heads), split along the
+// sequence ("flash-decode").
+//
+// Bound: HBM/L2 bandwidth on the cached K and V rows: algorithmic bytes per launch =
+// (pos + 1) * 2 * n_kv_heads * head_dim * 2.  At the context lengths of the benchmark configs
+// this is 1-4 % of a layer's weight bytes, so the kernel is shaped for latency: many small
+// CTAs, one pass, no N x N score buffer.
+//
+//   grid   (n_splits, n_kv_heads); CTA (s, g) handles cache rows [s*split_len, (s+1)*split_len)
+//          of KV head g for all `G` query heads of that group, so K and V are read once per
+//          group, not once per query head.
+//   block  128 threads.  Scores: thread t owns cache row t of the tile and computes the G dot
+//          products in FP32 ascending d, the order of the reference (inference.cu:776-778),
+//          from a 16-byte-chunk XOR-swizzled shared-memory tile (conflict-free row reads).
+//          P.V: thread t owns output dimension t % head_dim.
+//   merge  each CTA writes (max, sum, unnormalised out) per query head to scratch; the last
+//          CTA to finish for a KV head (atomic counter) rescales and adds the partials in split
+//          order, normalises and writes FP16 (inference.cu:945).  The counter is left at zero.
+#include "common.cuh"
+
+namespace llmb {
+
+constexpr int kAttnThreads = 128;
+constexpr int kTile = 128;
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+struct AttnParams {
+    const __half *q;
+    const __half *k_cache;
+    const __half *v_cache;
+    const int *pos;
+    __half *out;
+    int *counters;   // [n_kv_heads]
+    float *part_ml;  // [n_kv_heads][n_splits][G][2]
+    float *part_o;   // [n_kv_heads][n_splits][G][HD]
+    int n_kv_heads, n_splits, split_len;
+};
+
+template <int HD, int G>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnParams p) {
+    constexpr int CHUNKS = HD / 8;              // 16-byte chunks per row
+    constexpr int DGROUPS = kAttnThreads / HD;  // thread groups that share one output dim
+    constexpr int HPT = G / DGROUPS;            // query heads per thread in the P.V phase
+    static_assert(G % DGROUPS == 0 && HPT >= 1, "group size must fill the block");
+    extern __shared__ __align__(128) unsigned char attn_smem[];
+    __half *k_tile = reinterpret_cast<__half *>(attn_smem);
+    __half *v_tile = k_tile + kTile * HD;
+    __shared__ __align__(16) float q_s[G * HD];
+    __shared__ __align__(16) float p_s[kTile * G];
+    __shared__ float red_max[4][G];
+    __shared__ float red_sum[4][G];
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, g = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int len_total = *p.pos + 1;
+    const int begin = split * p.split_len;
+    const int end = min(begin + p.split_len, len_total);
+    const size_t row_stride = (size_t)p.n_kv_heads * HD;
+    const float inv_den = sqrtf((float)HD);
+
+    for (int i = tid; i < G * HD; i += kAttnThreads) q_s[i] = __half2float(p.q[(size_t)g * G * HD + i]);
+
+    float m_run[G], l_run[G], acc[HPT];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.0f;
+    }
+#pragma unroll
+    for (int h = 0; h < HPT; ++h) acc[h] = 0.0f;
+    const int my_d = tid % HD;
+    const int my_h0 = (DGROUPS == 1) ? 0 : (tid / HD) * HPT;
+
+    for (int t0 = begin; t0 < end; t0 += kTile) {
+        const int rows = min(kTile, end - t0);
+        __syncthreads();  // previous tile fully consumed (also publishes q_s)
+        for (int c = tid; c < rows * CHUNKS; c += kAttnThreads) {
+            const int r = c / CHUNKS, ch = c % CHUNKS;
+            const int sw = ch ^ (r & 7);
+            const size_t goff = (size_t)(t0 + r) * row_stride + (size_t)g * HD + ch * 8;
+            cp_async16(&k_tile[r * HD + sw * 8], p.k_cache + goff);
+            cp_async16(&v_tile[r * HD + ch * 8], p.v_cache + goff);
+        }
+        cp_async_wait_all();
+        __syncthreads();
+
+        // scores for cache row t0 + tid
+        float s[G];
+        const bool active = tid < rows;
+#pragma unroll
+        for (int h = 0; h < G; ++h) s[h] = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int ch = 0; ch < CHUNKS; ++ch) {
+                const uint4 kv = *reinterpret_cast<const uint4 *>(&k_tile[tid * HD + ((ch ^ (tid & 7)) * 8)]);
+                const __half2 *kh = reinterpret_cast<const __half2 *>(&kv);
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float2 f = __half22float2(kh[e]);
+                    kf[2 * e] = f.x;
+                    kf[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
+                    const float4 qa = *reinterpret_cast<const float4 *>(&q_s[h * HD + ch * 8]);
+                    const float4 qb = *reinterpret_cast<const float4 *>(&q_s[h * HD + ch * 8 + 4]);
+                    s[h] = fmaf(qa.x, kf[0], s[h]);
+                    s[h] = fmaf(qa.y, kf[1], s[h]);
+                    s[h] = fmaf(qa.z, kf[2], s[h]);
+                    s[h] = fmaf(qa.w, kf[3], s[h]);
+                    s[h] = fmaf(qb.x, kf[4], s[h]);
+                    s[h] = fmaf(qb.y, kf[5], s[h]);
+                    s[h] = fmaf(qb.z, kf[6], s[h]);
+                    s[h] = fmaf(qb.w, kf[7], s[h]);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < G; ++h) s[h] = __fdiv_rn(s[h], inv_den);  // inference.cu:784
+        } else {
+#pragma unroll
+            for (int h = 0; h < G; ++h) s[h] = -INFINITY;
+        }
+        // tile maximum per head
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float mx = warp_max(s[h]);
+            if (lane == 0) red_max[warp][h] = mx;
+        }
+        __syncthreads();
+        float scale[G];
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float mx = fmaxf(fmaxf(red_max[0][h], red_max[1][h]), fmaxf(red_max[2][h], red_max[3][h]));
+            float m_new = fmaxf(m_run[h], mx);
+            scale[h] = (m_run[h] == -INFINITY) ? 0.0f : expf(m_run[h] - m_new);
+            m_run[h] = m_new;
+            float pv = active ? expf(s[h] - m_new) : 0.0f;
+            l_run[h] = l_run[h] * scale[h] + pv;  // per-thread partial of the softmax denominator
+            p_s[tid * G + h] = pv;
+        }
+        __syncthreads();
+        // P.V for this tile
+#pragma unroll
+        for (int h = 0; h < HPT; ++h) acc[h] *= scale[my_h0 + h];
+        for (int r = 0; r < rows; ++r) {
+            const float vf = __half2float(v_tile[r * HD + my_d]);
+#pragma unroll
+            for (int h = 0; h < HPT; ++h) acc[h] = fmaf(p_s[r * G + my_h0 + h], vf, acc[h]);
+        }
+    }
+
+    // CTA totals: denominators across threads, then publish the partial.
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        float sm = warp_sum(l_run[h]);
+        if (lane == 0) red_sum[warp][h] = sm;
+    }
+    __syncthreads();
+    const size_t pbase = ((size_t)g * p.n_splits + split) * G;
+    if (tid < G) {
+        const float l = (red_sum[0][tid] + red_sum[1][tid]) + (red_sum[2][tid] + red_sum[3][tid]);
+        float m = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+            if (h == tid) m = m_run[h];
+        p.part_ml[(pbase + tid) * 2] = m;
+        p.part_ml[(pbase + tid) * 2 + 1] = l;
+    }
+#pragma unroll
+    for (int h = 0; h < HPT; ++h) p.part_o[(pbase + my_h0 + h) * HD + my_d] = acc[h];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(&p.counters[g], 1);
+        is_last = (prev == p.n_splits - 1);
+        if (is_last) p.counters[g] = 0;  // every split has arrived; ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    // Merge, in split order.
+    const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
+    const size_t gbase = (size_t)g * p.n_splits * G;
+#pragma unroll
+    for (int h = 0; h < HPT; ++h) {
+        const int head = my_h0 + h;
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < n_used; ++sidx)
+            M = fmaxf(M, __ldcg(&p.part_ml[(gbase + (size_t)sidx * G + head) * 2]));
+        float num = 0.0f, den = 0.0f;
+        for (int sidx = 0; sidx < n_used; ++sidx) {
+            const size_t pi = gbase + (size_t)sidx * G + head;
+            const float m = __ldcg(&p.part_ml[pi * 2]);
+            const float l = __ldcg(&p.part_ml[pi * 2 + 1]);
+            const float wgt = (m == -INFINITY) ? 0.0f : expf(m - M);
+            num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + my_d]), num);
+            den = fmaf(wgt, l, den);
+        }
+        p.out[((size_t)g * G + head) * HD + my_d] = __float2half_rn(__fdiv_rn(num, den));
+    }
+}
+
+template <int HD, int G>
+static int launch_attn(const AttnParams &p, bool pdl, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)2 * kTile * HD * sizeof(__half);
+    static bool attr_set = false;
+    if (!attr_set) {
+        LLMB_CUDA_OK(cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+        attr_set = true;
+    }
+    LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads), dim3(kAttnThreads), smem,
+                            stream, pdl, p));
+    return LLMB_OK;
+}
+
+static size_t attn_counters_bytes(int n_kv_heads) { return ((size_t)n_kv_heads * 4 + 255) / 256 * 256; }
+
+}  // namespace llmb
+
+extern "C" size_t llmb_attn_decode_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int n_splits) {
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_splits <= 0) return 0;
+    size_t ml = ((size_t)n_q_heads * n_splits * 2 * 4 + 255) / 256 * 256;
+    size_t o = (size_t)n_q_heads * n_splits * head_dim * 4;
+    return llmb::attn_counters_bytes(n_kv_heads) + ml + o;
+}
+
+extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                                const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
+                                int split_len, uint16_t *d_out, void *d_scratch, int use_pdl, llmb_stream_t stream_) {
+    using namespace llmb;
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !d_scratch) return LLMB_ERR_INVALID;
+    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads || n_splits <= 0 || split_len <= 0) return LLMB_ERR_INVALID;
+    if (((uintptr_t)d_scratch & 255) || ((uintptr_t)d_k_cache & 15) || ((uintptr_t)d_v_cache & 15))
+        return LLMB_ERR_INVALID;
+    AttnParams p;
+    p.q = reinterpret_cast<const __half *>(d_q);
+    p.k_cache = reinterpret_cast<const __half *>(d_k_cache);
+    p.v_cache = reinterpret_cast<const __half *>(d_v_cache);
+    p.pos = d_pos;
+    p.out = reinterpret_cast<__half *>(d_out);
+    unsigned char *sc = static_cast<unsigned char *>(d_scratch);
+    p.counters = reinterpret_cast<int *>(sc);
+    sc += attn_counters_bytes(n_kv_heads);
+    p.part_ml = reinterpret_cast<float *>(sc);
+    sc += ((size_t)n_q_heads * n_splits * 2 * 4 + 255) / 256 * 256;
+    p.part_o = reinterpret_cast<float *>(sc);
+    p.n_kv_heads = n_kv_heads;
+    p.n_splits = n_splits;
+    p.split_len = split_len;
+    const int G = n_q_heads / n_kv_heads;
+    const bool pdl = use_pdl != 0;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (head_dim == 128) {
+        switch (G) {
+            case 1: return launch_attn<128, 1>(p, pdl, stream);
+            case 2: return launch_attn<128, 2>(p, pdl, stream);
+            case 4: return launch_attn<128, 4>(p, pdl, stream);
+            case 8: return launch_attn<128, 8>(p, pdl, stream);
+        }
+    } else if (head_dim == 64) {
+        switch (G) {
+            case 2: return launch_attn<64, 2>(p, pdl, stream);
+            case 4: return launch_attn<64, 4>(p, pdl, stream);
+            case 8: return launch_attn<64, 8>(p, pdl, stream);
+        }
+    }
+    return LLMB_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,125 @@
+"""Thin Python handles over the host surface of include/llama3.h (same call order as the
+reference driver src/main.cu:61-123)."""
+import ctypes as C
+
+import numpy as np
+
+from . import Llama3Config, TensorStruct, check, lib
+
+
+def _cfg_struct(cfg, max_seq):
+    return Llama3Config(cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, max_seq,
+                        cfg.rope_theta, cfg.eps)
+
+
+class Model:
+    """init_llama3 -> load_safetensor_weights* -> to_cuda, or init_llama3 -> synthetic weights."""
+
+    def __init__(self, n_layers):
+        self.ptr = lib.init_llama3(n_layers)
+        if not self.ptr:
+            raise MemoryError("init_llama3 failed")
+
+    @classmethod
+    def from_safetensors(cls, cfg, paths, max_seq=2048):
+        m = cls(cfg.n_layers)
+        partial = Llama3Config(0, 0, 0, cfg.head_dim, 0, 0, max_seq, cfg.rope_theta, cfg.eps)
+        check(lib.llama3_set_config(m.ptr, C.byref(partial)), "llama3_set_config")
+        for p in paths:
+            check(lib.llama3_load_safetensors(m.ptr, str(p).encode()), "load_safetensor_weights")
+        check(lib.llama3_to_cuda(m.ptr), "to_cuda")
+        return m
+
+    @classmethod
+    def synthetic(cls, cfg, seed=0, max_seq=2048):
+        m = cls(cfg.n_layers)
+        c = _cfg_struct(cfg, max_seq)
+        check(lib.llama3_synth_weights(m.ptr, C.byref(c), seed, 1 if cfg.bf16_weights else 0), "llama3_synth_weights")
+        return m
+
+    @property
+    def config(self):
+        return self.ptr.contents.config
+
+    def tensor_ptr(self, name, layer=None):
+        """Device address of a weight tensor (FP16)."""
+        if layer is None:
+            t = getattr(self.ptr.contents, name)
+        else:
+            t = getattr(self.ptr.contents.layers[layer].contents, name)
+        return t.contents.d_fp16_tensor
+
+    def close(self):
+        if self.ptr:
+            lib.free_llama3(self.ptr)
+            self.ptr = None
+
+
+class Cache:
+    """init_cache + inference(): KV cache, scratch and the captured decode step."""
+
+    def __init__(self, model):
+        self.model = model
+        rc = C.c_int(0)
+        self.ptr = lib.llama3_init_cache(model.ptr, C.byref(rc))
+        if not self.ptr:
+            check(rc.value or 1, "init_cache")
+        self.vocab = model.config.vocab
+        self.max_seq = model.config.max_seq
+        self._tokens = (C.c_int * (self.max_seq + 2))()
+        self._x = TensorStruct()
+        self._d_tokens = None
+
+    def set_options(self, use_graph=-1, use_pdl=-1, copy_logits=-1):
+        check(lib.cache_set_options(self.ptr, int(use_graph), int(use_pdl), int(copy_logits)), "cache_set_options")
+
+    def reset(self):
+        check(lib.cache_reset(self.ptr), "cache_reset")
+
+    def infer(self, token_ids):
+        """One reference-style inference() call on the whole id list; returns the next token."""
+        n = len(token_ids)
+        self._tokens[0] = n + 1
+        self._tokens[1:n + 1] = [int(t) for t in token_ids]
+        r = lib.inference(self.model.ptr, C.byref(self._x), self._d_tokens, self._tokens, self.ptr)
+        if r < 0:
+            check(-r, "inference")
+        return r
+
+    def logits(self):
+        """FP16 logits of the last inference() call as a numpy uint16 bit-pattern array."""
+        buf = (C.c_uint16 * self.vocab).from_address(self.ptr.contents.h_token_probdist)
+        return np.frombuffer(buf, dtype=np.uint16).copy()
+
+    def enable_hidden_dump(self, on=True):
+        check(lib.cache_enable_hidden_dump(self.ptr, 1 if on else 0), "cache_enable_hidden_dump")
+
+    def hidden(self):
+        cfg = self.model.config
+        out = np.empty((self.model.ptr.contents.n_layers + 1, cfg.d_model), dtype=np.uint16)
+        check(lib.cache_read_hidden(self.ptr, out.ctypes.data), "cache_read_hidden")
+        return out
+
+    def greedy(self, prompt, n_new):
+        """Device-resident greedy generation; returns (tokens, prefill_ms, decode_ms)."""
+        p = (C.c_int * len(prompt))(*[int(t) for t in prompt])
+        out = (C.c_int * n_new)()
+        pre, dec = C.c_float(0), C.c_float(0)
+        check(lib.inference_greedy(self.model.ptr, self.ptr, p, len(prompt), n_new, out, C.byref(pre), C.byref(dec)),
+              "inference_greedy")
+        return list(out), pre.value, dec.value
+
+    def continue_greedy(self, n_steps):
+        """n_steps more device-resident greedy steps from the current state; returns (tokens, ms)."""
+        out = (C.c_int * n_steps)()
+        ms = C.c_float(0)
+        check(lib.inference_continue(self.model.ptr, self.ptr, n_steps, out, C.byref(ms)), "inference_continue")
+        return list(out), ms.value
+
+    def kernel_launches(self):
+        return lib.cache_kernel_launches(self.ptr)
+
+    def close(self):
+        if self.ptr:
+            lib.free_cache(self.ptr)
+            self.ptr = None

@@ -1,0 +1,518 @@
+// The per-token forward loop: the reference's src/inference/inference.cu re-built on the fused
+// sm_100a kernels, behind the same entry points (init_cache, inference) plus tokens_to_cuda
+// (src/tokenizer/tokenizer.cu:157-198).
+//
+// One decode step = 1 + 5 * n_layers + 2 kernels, captured once per KV-length bucket into a
+// CUDA graph with programmatic-dependent-launch edges and replayed:
+//
+//   embed_rope                         x = Embed[token]; RoPE angles of this position
+//   per layer:
+//     gemv RMSNORM -> ROPE_KV          input_layernorm + q/k/v projections + RoPE + cache append
+//     attn_decode                      softmax(q K^T / sqrt(hd)) V over cache rows 0..pos
+//     gemv -> RESIDUAL                 o_proj + residual add
+//     gemv RMSNORM -> SWIGLU           post_attention_layernorm + gate/up + SiLU(gate)*up
+//     gemv -> RESIDUAL                 down_proj + residual add
+//   gemv RMSNORM -> STORE              final norm + lm_head -> FP16 logits
+//   argmax                             greedy token, position += 1, token appended to the history
+//
+// The token id and the position live in device memory, so the same graph serves every step and a
+// run of steps needs no host round trip (inference_greedy).  The reference issues 483 launches,
+// 96 16-MiB copies and 419 device synchronisations per token (inference.cu:149-193).
+//
+// KV cache: K and V are [n_layers][max_seq][n_kv_heads * head_dim] FP16, K stored after RoPE:
+// the reference's row layout (inference.cu:761-768, :926) with a layer axis added.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <vector>
+
+#include "../csrc/common.cuh"
+#include "../../include/llama3.h"
+#include "host_internal.h"
+
+using namespace llmb;
+
+namespace {
+
+__global__ void set_int_kernel(int *dst, int value) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *dst = value;
+}
+
+struct Engine {
+    Llama3 *model = nullptr;
+    cudaStream_t stream = nullptr;
+    int d = 0, nq = 0, nkv = 0, hd = 0, ffn = 0, vocab = 0, embed_rows = 0, layers = 0, max_seq = 0;
+    __half *x = nullptr, *q = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr;
+    __half *kcache = nullptr, *vcache = nullptr;
+    float *rope_cs = nullptr;
+    int *d_pos = nullptr, *d_next = nullptr, *d_history = nullptr;
+    void *attn_scratch = nullptr;
+    int max_splits = 0;
+    int *h_next = nullptr;  // pinned
+    __half *hidden = nullptr;
+    bool use_graph = true, use_pdl = true, copy_logits = true, hidden_dump = false;
+    bool greedy_state = false;  // device history[consumed.size()] holds a sampled token not yet fed
+    std::vector<int> consumed;  // ids whose K/V rows are in the cache
+    std::map<int, cudaGraphExec_t> graphs;  // key: bucket * 2 + with_logits
+    long long launches = 0;
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+};
+
+inline Engine *eng(const CudaCache *c) { return c ? static_cast<Engine *>(c->priv) : nullptr; }
+
+struct SplitPlan {
+    int bucket, n_splits, split_len;
+};
+
+// Attention split geometry for a sequence of `len` cached rows.  The grid is baked into a
+// captured graph, so lengths are bucketed to powers of two (>= 512).
+SplitPlan plan_splits(int len) {
+    int bucket = 512;
+    while (bucket < len) bucket <<= 1;
+    int split_len = bucket / 16;
+    if (split_len > 128) split_len = 128;
+    return {bucket, bucket / split_len, split_len};
+}
+
+int enqueue_step(Engine *e, bool with_logits, const SplitPlan &sp) {
+    Llama3 *m = e->model;
+    const Llama3Config &c = m->config;
+    cudaStream_t s = e->stream;
+    const int pdl = e->use_pdl ? 1 : 0;
+    int rc = llmb_embed_rope(reinterpret_cast<const uint16_t *>(m->embed_tokens->d_fp16_tensor), e->d_history, e->d_pos,
+                             1, e->d, e->embed_rows, e->hd, c.rope_theta, reinterpret_cast<uint16_t *>(e->x),
+                             e->rope_cs, 1 /* token = history[pos] */, pdl, s);
+    if (rc) return rc;
+    if (e->hidden_dump)
+        LLMB_CUDA_OK(cudaMemcpyAsync(e->hidden, e->x, (size_t)e->d * 2, cudaMemcpyDeviceToDevice, s));
+    const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    for (int l = 0; l < e->layers; ++l) {
+        const Llama3Layer *L = m->layers[l];
+        __half *kl = e->kcache + (size_t)l * e->max_seq * n_kv;
+        __half *vl = e->vcache + (size_t)l * e->max_seq * n_kv;
+        LlmbGemvArgs a = {};
+        a.use_pdl = pdl;
+        // input_layernorm + QKV + RoPE + cache append
+        a.w = reinterpret_cast<const uint16_t *>(L->self_attn_q_proj->d_fp16_tensor);
+        a.x = reinterpret_cast<const uint16_t *>(e->x);
+        a.y = reinterpret_cast<uint16_t *>(e->q);
+        a.n = n_q + 2 * n_kv;
+        a.k = e->d;
+        a.prologue = LLMB_PRO_RMSNORM;
+        a.gamma = reinterpret_cast<const uint16_t *>(L->input_layernorm->d_fp16_tensor);
+        a.eps = c.eps;
+        a.epilogue = LLMB_EPI_ROPE_KV;
+        a.n_q = n_q;
+        a.n_kv = n_kv;
+        a.head_dim = e->hd;
+        a.rope_cs = e->rope_cs;
+        a.k_cache = reinterpret_cast<uint16_t *>(kl);
+        a.v_cache = reinterpret_cast<uint16_t *>(vl);
+        a.pos = e->d_pos;
+        a.max_pos = e->max_seq;
+        if ((rc = llmb_gemv_f16(&a, s))) return rc;
+        if ((rc = llmb_attn_decode(reinterpret_cast<const uint16_t *>(e->q), reinterpret_cast<const uint16_t *>(kl),
+                                   reinterpret_cast<const uint16_t *>(vl), e->d_pos, e->nq, e->nkv, e->hd, sp.n_splits,
+                                   sp.split_len, reinterpret_cast<uint16_t *>(e->attn), e->attn_scratch, pdl, s)))
+            return rc;
+        // o_proj + residual
+        LlmbGemvArgs o = {};
+        o.use_pdl = pdl;
+        o.w = reinterpret_cast<const uint16_t *>(L->self_attn_o_proj->d_fp16_tensor);
+        o.x = reinterpret_cast<const uint16_t *>(e->attn);
+        o.y = reinterpret_cast<uint16_t *>(e->x);
+        o.n = e->d;
+        o.k = n_q;
+        o.epilogue = LLMB_EPI_RESIDUAL;
+        if ((rc = llmb_gemv_f16(&o, s))) return rc;
+        // post_attention_layernorm + gate/up + SwiGLU
+        LlmbGemvArgs f = {};
+        f.use_pdl = pdl;
+        f.w = reinterpret_cast<const uint16_t *>(L->mlp_gate_proj->d_fp16_tensor);
+        f.w2 = reinterpret_cast<const uint16_t *>(L->mlp_up_proj->d_fp16_tensor);
+        f.x = reinterpret_cast<const uint16_t *>(e->x);
+        f.y = reinterpret_cast<uint16_t *>(e->h);
+        f.n = e->ffn;
+        f.k = e->d;
+        f.prologue = LLMB_PRO_RMSNORM;
+        f.gamma = reinterpret_cast<const uint16_t *>(L->post_attention_layernorm->d_fp16_tensor);
+        f.eps = c.eps;
+        f.epilogue = LLMB_EPI_SWIGLU;
+        if ((rc = llmb_gemv_f16(&f, s))) return rc;
+        // down_proj + residual
+        LlmbGemvArgs dn = {};
+        dn.use_pdl = pdl;
+        dn.w = reinterpret_cast<const uint16_t *>(L->mlp_down_proj->d_fp16_tensor);
+        dn.x = reinterpret_cast<const uint16_t *>(e->h);
+        dn.y = reinterpret_cast<uint16_t *>(e->x);
+        dn.n = e->d;
+        dn.k = e->ffn;
+        dn.epilogue = LLMB_EPI_RESIDUAL;
+        if ((rc = llmb_gemv_f16(&dn, s))) return rc;
+        if (e->hidden_dump)
+            LLMB_CUDA_OK(cudaMemcpyAsync(e->hidden + (size_t)(l + 1) * e->d, e->x, (size_t)e->d * 2,
+                                         cudaMemcpyDeviceToDevice, s));
+    }
+    if (with_logits) {
+        LlmbGemvArgs lm = {};
+        lm.use_pdl = pdl;
+        lm.w = reinterpret_cast<const uint16_t *>(m->lm_head->d_fp16_tensor);
+        lm.x = reinterpret_cast<const uint16_t *>(e->x);
+        lm.y = reinterpret_cast<uint16_t *>(e->logits);
+        lm.n = e->vocab;
+        lm.k = e->d;
+        lm.prologue = LLMB_PRO_RMSNORM;
+        lm.gamma = reinterpret_cast<const uint16_t *>(m->norm->d_fp16_tensor);
+        lm.eps = c.eps;
+        lm.epilogue = LLMB_EPI_STORE;
+        if ((rc = llmb_gemv_f16(&lm, s))) return rc;
+        if ((rc = llmb_argmax_f16(reinterpret_cast<const uint16_t *>(e->logits), e->vocab, e->d_next, e->d_pos,
+                                  e->d_history, e->max_seq, pdl, s)))
+            return rc;
+    } else {
+        if ((rc = llmb_advance_pos(e->d_pos, pdl, s))) return rc;
+    }
+    return LLMB_OK;
+}
+
+int kernels_per_step(const Engine *e, bool with_logits) { return 1 + 5 * e->layers + (with_logits ? 2 : 1); }
+
+// Runs one step for the token at history[pos]; `len` = pos + 1 is known on the host.
+int run_step(Engine *e, bool with_logits, int len) {
+    const SplitPlan sp = plan_splits(len);
+    e->launches += kernels_per_step(e, with_logits);
+    if (!e->use_graph || e->hidden_dump) return enqueue_step(e, with_logits, sp);
+    const int key = sp.bucket * 2 + (with_logits ? 1 : 0);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        cudaGraph_t graph = nullptr;
+        LLMB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_step(e, with_logits, sp);
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+        if (rc) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        LLMB_CUDA_OK(ce);
+        cudaGraphExec_t exec = nullptr;
+        ce = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        LLMB_CUDA_OK(ce);
+        it = e->graphs.emplace(key, exec).first;
+    }
+    LLMB_CUDA_OK(cudaGraphLaunch(it->second, e->stream));
+    return LLMB_OK;
+}
+
+int set_device_int(Engine *e, int *dst, int value) {
+    LLMB_CUDA_OK(launch_pdl(set_int_kernel, dim3(1), dim3(1), 0, e->stream, false, dst, value));
+    return LLMB_OK;
+}
+
+// Feeds ids[from..to) (history rows from..to-1), logits only for the last one.
+int feed_tokens(Engine *e, const int *ids, int from, int to) {
+    if (to <= from) return LLMB_ERR_INVALID;
+    if (to > e->max_seq) {
+        set_last_error("inference: sequence longer than the KV cache (config.max_seq)");
+        return LLMB_ERR_INVALID;
+    }
+    // pageable source: the runtime stages it before returning, so `ids` may change afterwards
+    LLMB_CUDA_OK(cudaMemcpyAsync(e->d_history + from, ids + from, sizeof(int) * (size_t)(to - from),
+                                 cudaMemcpyHostToDevice, e->stream));
+    int rc = set_device_int(e, e->d_pos, from);
+    if (rc) return rc;
+    for (int p = from; p < to; ++p)
+        if ((rc = run_step(e, p == to - 1, p + 1))) return rc;
+    return LLMB_OK;
+}
+
+void destroy_engine(Engine *e) {
+    if (!e) return;
+    for (auto &kv : e->graphs) cudaGraphExecDestroy(kv.second);
+    cudaFree(e->x); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->h);
+    cudaFree(e->rope_cs); cudaFree(e->d_pos); cudaFree(e->d_next); cudaFree(e->d_history);
+    cudaFree(e->attn_scratch); cudaFree(e->hidden);
+    if (e->h_next) cudaFreeHost(e->h_next);
+    for (auto &ev : e->ev)
+        if (ev) cudaEventDestroy(ev);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+Tensor *make_view_tensor(int rows, int cols, __half *data) {
+    Tensor *t = static_cast<Tensor *>(calloc(1, sizeof(Tensor)));
+    if (!t) return nullptr;
+    t->ndim = static_cast<int *>(malloc(sizeof(int)));
+    t->mem_len = static_cast<int *>(malloc(sizeof(int)));
+    t->shape = static_cast<int *>(malloc(2 * sizeof(int)));
+    if (!t->ndim || !t->mem_len || !t->shape) return t;
+    *t->ndim = 2;
+    t->shape[0] = rows;
+    t->shape[1] = cols;
+    long long n = (long long)rows * cols;
+    *t->mem_len = n > 0x7fffffffLL ? 0x7fffffff : (int)n;
+    t->d_fp16_tensor = data;
+    t->loaded = 1;
+    return t;
+}
+
+}  // namespace
+
+extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
+    auto fail = [&](int code, const char *msg) -> CudaCache * {
+        if (msg) set_last_error(msg);
+        if (status_out) *status_out = code;
+        return nullptr;
+    };
+    if (!m || !m->config_ready) return fail(LLMB_ERR_INVALID, "init_cache: call to_cuda first");
+    const Llama3Config &c = m->config;
+    Engine *e = new Engine();
+    e->model = m;
+    e->d = c.d_model;
+    e->nq = c.n_q_heads;
+    e->nkv = c.n_kv_heads;
+    e->hd = c.head_dim;
+    e->ffn = c.ffn;
+    e->vocab = c.vocab;
+    e->embed_rows = m->embed_tokens->shape[0];
+    e->layers = m->n_layers;
+    e->max_seq = c.max_seq;
+    const size_t n_q = (size_t)e->nq * e->hd, n_kv = (size_t)e->nkv * e->hd;
+    const size_t kv_elems = (size_t)e->layers * e->max_seq * n_kv;
+    e->max_splits = plan_splits(e->max_seq).n_splits;
+    const size_t scratch = llmb_attn_decode_scratch_bytes(e->nq, e->nkv, e->hd, e->max_splits);
+    cudaError_t ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    auto alloc = [&](void **p, size_t bytes) {
+        if (ce == cudaSuccess) ce = cudaMalloc(p, bytes);
+        if (ce == cudaSuccess) ce = cudaMemset(*p, 0, bytes);
+    };
+    alloc(reinterpret_cast<void **>(&e->x), (size_t)e->d * 2);
+    alloc(reinterpret_cast<void **>(&e->q), n_q * 2);
+    alloc(reinterpret_cast<void **>(&e->attn), n_q * 2);
+    alloc(reinterpret_cast<void **>(&e->h), (size_t)e->ffn * 2);
+    alloc(reinterpret_cast<void **>(&e->logits), (size_t)e->vocab * 2);
+    alloc(reinterpret_cast<void **>(&e->kcache), kv_elems * 2);
+    alloc(reinterpret_cast<void **>(&e->vcache), kv_elems * 2);
+    alloc(reinterpret_cast<void **>(&e->rope_cs), (size_t)e->hd * 4);
+    alloc(reinterpret_cast<void **>(&e->d_pos), 256);
+    alloc(reinterpret_cast<void **>(&e->d_next), 256);
+    alloc(reinterpret_cast<void **>(&e->d_history), sizeof(int) * ((size_t)e->max_seq + 1));
+    alloc(&e->attn_scratch, scratch);
+    if (ce == cudaSuccess) ce = cudaMallocHost(reinterpret_cast<void **>(&e->h_next), 256);
+    for (auto &ev : e->ev)
+        if (ce == cudaSuccess) ce = cudaEventCreate(&ev);
+    CudaCache *cache = static_cast<CudaCache *>(calloc(1, sizeof(CudaCache)));
+    llmb_half *h_logits = nullptr;
+    if (ce == cudaSuccess) ce = cudaMallocHost(reinterpret_cast<void **>(&h_logits), (size_t)e->vocab * 2);
+    if (ce != cudaSuccess || !cache) {
+        int code = ce != cudaSuccess ? cuda_fail(ce, __FILE__, __LINE__) : LLMB_ERR_NOMEM;
+        cudaFree(e->logits); cudaFree(e->kcache); cudaFree(e->vcache);
+        if (h_logits) cudaFreeHost(h_logits);
+        destroy_engine(e);
+        free(cache);
+        return fail(code, nullptr);
+    }
+    cache->priv = e;
+    cache->PN_X = nullptr;
+    cache->Q = make_view_tensor(1, (int)n_q, e->q);
+    cache->K = make_view_tensor(e->layers * e->max_seq, (int)n_kv, e->kcache);
+    cache->V = make_view_tensor(e->layers * e->max_seq, (int)n_kv, e->vcache);
+    cache->d_attention_score_cache = nullptr;
+    cache->d_feedforward_cache_upgate = e->h;
+    cache->d_token_probdist = e->logits;
+    cache->h_token_probdist = h_logits;
+    cache->f_token_probdist = static_cast<float *>(malloc(sizeof(float) * (size_t)e->vocab));
+    if (status_out) *status_out = LLMB_OK;
+    return cache;
+}
+
+extern "C" CudaCache *init_cache(Llama3 *m) {
+    int rc = 0;
+    CudaCache *c = llama3_init_cache(m, &rc);
+    if (!c) {
+        printf("Error: init_cache failed (%d): %s\n", rc, llmb_last_error());
+        exit(EXIT_FAILURE);  // CHECK_CUDA_ERROR in the reference exits (inference.cu:13-21)
+    }
+    return c;
+}
+
+extern "C" void free_cache(CudaCache *cache) {
+    if (!cache) return;
+    Engine *e = eng(cache);
+    if (e) {
+        cudaStreamSynchronize(e->stream);
+        cudaFree(e->logits);
+        cudaFree(e->kcache);
+        cudaFree(e->vcache);
+        destroy_engine(e);
+    }
+    auto free_view = [](Tensor *t) {
+        if (!t) return;
+        free(t->ndim); free(t->mem_len); free(t->shape); free(t);
+    };
+    free_view(cache->Q);
+    free_view(cache->K);
+    free_view(cache->V);
+    if (cache->h_token_probdist) cudaFreeHost(cache->h_token_probdist);
+    free(cache->f_token_probdist);
+    free(cache);
+}
+
+extern "C" int cache_reset(CudaCache *cache) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    e->consumed.clear();
+    e->greedy_state = false;
+    return LLMB_OK;
+}
+
+extern "C" int cache_set_options(CudaCache *cache, int use_graph, int use_pdl, int copy_logits) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    if (use_graph >= 0) e->use_graph = use_graph != 0;
+    if (use_pdl >= 0 && (use_pdl != 0) != e->use_pdl) {
+        e->use_pdl = use_pdl != 0;
+        for (auto &kv : e->graphs) cudaGraphExecDestroy(kv.second);
+        e->graphs.clear();
+    }
+    if (copy_logits >= 0) e->copy_logits = copy_logits != 0;
+    return LLMB_OK;
+}
+
+extern "C" int cache_enable_hidden_dump(CudaCache *cache, int enable) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    if (enable && !e->hidden) LLMB_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&e->hidden), (size_t)(e->layers + 1) * e->d * 2));
+    e->hidden_dump = enable != 0;
+    return LLMB_OK;
+}
+
+extern "C" int cache_read_hidden(CudaCache *cache, uint16_t *h_out) {
+    Engine *e = eng(cache);
+    if (!e || !e->hidden || !h_out) return LLMB_ERR_INVALID;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    LLMB_CUDA_OK(cudaMemcpy(h_out, e->hidden, (size_t)(e->layers + 1) * e->d * 2, cudaMemcpyDeviceToHost));
+    return LLMB_OK;
+}
+
+extern "C" long long cache_kernel_launches(const CudaCache *cache) {
+    const Engine *e = eng(cache);
+    return e ? e->launches : -1;
+}
+
+// tokenizer.cu:157-198: allocates the caller-owned activation tensor X [2048][embed_size] (zeroed)
+// and the device token array.  The fused engine keeps its residual stream in its own buffer, so X
+// only exists for callers that free it with _free_tensor as src/main.cu:124 does.
+extern "C" int *tokens_to_cuda(int *tokens, int embed_size, Tensor *X) {
+    (void)tokens;
+    if (!X || embed_size <= 0) return nullptr;
+    memset(X, 0, sizeof(Tensor));
+    X->ndim = static_cast<int *>(malloc(sizeof(int)));
+    X->mem_len = static_cast<int *>(malloc(sizeof(int)));
+    X->shape = static_cast<int *>(malloc(sizeof(int) * 2));
+    if (!X->ndim || !X->mem_len || !X->shape) return nullptr;
+    *X->ndim = 2;
+    *X->mem_len = embed_size * 2048;
+    X->shape[0] = 2048;
+    X->shape[1] = embed_size;
+    void *p = nullptr;
+    if (cudaMalloc(&p, sizeof(__half) * (size_t)*X->mem_len) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(__half) * (size_t)*X->mem_len);
+    X->d_fp16_tensor = static_cast<llmb_half *>(p);
+    X->loaded = 1;
+    int *d_tokens = nullptr;
+    if (cudaMalloc(reinterpret_cast<void **>(&d_tokens), sizeof(int) * (2048 + 1)) != cudaSuccess) return nullptr;
+    return d_tokens;
+}
+
+extern "C" int inference(Llama3 *m, Tensor *X, int *d_tokens, int *h_tokens, CudaCache *cache) {
+    (void)X;
+    Engine *e = eng(cache);
+    if (!m || !e || !h_tokens || e->model != m) {
+        set_last_error("inference: null or mismatched model/cache");
+        return -LLMB_ERR_INVALID;
+    }
+    const int count = h_tokens[0] - 1;  // tokenizer.cu:152
+    if (count < 1 || count > e->max_seq) {
+        set_last_error("inference: token count outside [1, max_seq]");
+        return -LLMB_ERR_INVALID;
+    }
+    const int *ids = h_tokens + 1;
+    // Reuse the cached prefix if the caller only appended (src/main.cu:121-122); else start over.
+    int keep = (int)e->consumed.size();
+    if (keep >= count) keep = 0;
+    for (int i = 0; i < keep; ++i)
+        if (e->consumed[i] != ids[i]) { keep = 0; break; }
+    int rc = feed_tokens(e, ids, keep, count);
+    if (rc) return -rc;
+    // The reference copies the whole token array to the device on every call (inference.cu:150).
+    if (d_tokens && count + 1 <= 2049)
+        cudaMemcpyAsync(d_tokens, h_tokens, sizeof(int) * (size_t)(count + 1), cudaMemcpyHostToDevice, e->stream);
+    if (e->copy_logits)
+        cudaMemcpyAsync(cache->h_token_probdist, e->logits, (size_t)e->vocab * 2, cudaMemcpyDeviceToHost, e->stream);
+    cudaMemcpyAsync(e->h_next, e->d_next, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+    cudaError_t ce = cudaStreamSynchronize(e->stream);
+    if (ce != cudaSuccess) return -cuda_fail(ce, __FILE__, __LINE__);
+    e->consumed.assign(ids, ids + count);
+    e->greedy_state = true;  // the argmax kernel appended the sampled token to the device history
+    return e->h_next[0];
+}
+
+extern "C" int inference_greedy(Llama3 *m, CudaCache *cache, const int *prompt, int n_prompt, int n_new, int *out_tokens,
+                                float *prefill_ms, float *decode_ms) {
+    Engine *e = eng(cache);
+    if (!m || !e || e->model != m || !prompt || n_prompt < 1 || n_new < 1 || !out_tokens) return LLMB_ERR_INVALID;
+    if (n_prompt + n_new > e->max_seq) {
+        set_last_error("inference_greedy: prompt + new tokens exceed config.max_seq");
+        return LLMB_ERR_INVALID;
+    }
+    e->consumed.clear();
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[0], e->stream));
+    int rc = feed_tokens(e, prompt, 0, n_prompt);  // yields generated token 1 at history[n_prompt]
+    if (rc) return rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[1], e->stream));
+    for (int i = 1; i < n_new; ++i)
+        if ((rc = run_step(e, true, n_prompt + i))) return rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[2], e->stream));
+    LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + n_prompt, sizeof(int) * (size_t)n_new,
+                                 cudaMemcpyDeviceToHost, e->stream));
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if (prefill_ms) LLMB_CUDA_OK(cudaEventElapsedTime(prefill_ms, e->ev[0], e->ev[1]));
+    if (decode_ms) LLMB_CUDA_OK(cudaEventElapsedTime(decode_ms, e->ev[1], e->ev[2]));
+    // the cache now holds prompt + all but the last generated token
+    e->consumed.assign(prompt, prompt + n_prompt);
+    for (int i = 0; i + 1 < n_new; ++i) e->consumed.push_back(out_tokens[i]);
+    e->greedy_state = true;
+    return LLMB_OK;
+}
+
+extern "C" int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int *out_tokens, float *ms) {
+    Engine *e = eng(cache);
+    if (!m || !e || e->model != m || n_steps < 1 || !out_tokens) return LLMB_ERR_INVALID;
+    if (!e->greedy_state || e->consumed.empty()) {
+        set_last_error("inference_continue: no greedy run to continue");
+        return LLMB_ERR_INVALID;
+    }
+    const int P = (int)e->consumed.size();  // rows in the cache; history[P] is the next input
+    if (P + n_steps > e->max_seq) {
+        set_last_error("inference_continue: would run past config.max_seq");
+        return LLMB_ERR_INVALID;
+    }
+    int rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[0], e->stream));
+    for (int i = 0; i < n_steps; ++i)
+        if ((rc = run_step(e, true, P + i + 1))) return rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[1], e->stream));
+    std::vector<int> fed((size_t)n_steps);
+    LLMB_CUDA_OK(cudaMemcpyAsync(fed.data(), e->d_history + P, sizeof(int) * (size_t)n_steps, cudaMemcpyDeviceToHost,
+                                 e->stream));
+    LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + P + 1, sizeof(int) * (size_t)n_steps,
+                                 cudaMemcpyDeviceToHost, e->stream));
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if (ms) LLMB_CUDA_OK(cudaEventElapsedTime(ms, e->ev[0], e->ev[1]));
+    e->consumed.insert(e->consumed.end(), fed.begin(), fed.end());
+    return LLMB_OK;
+}

@@ -1,0 +1,365 @@
+// Model container and load-time upload: the reference's src/llama3/llama3.cu re-implemented.
+//
+//   init_llama3 / free_llama3 / _free_tensor   llama3.cu:9-154
+//   to_cuda                                    llama3.cu:156-238 (H2D + BF16->FP16 per tensor)
+//
+// Device layout chosen for the decode kernels (not the reference's one-allocation-per-tensor):
+//   * q_proj, k_proj, v_proj of a layer live back to back in ONE buffer [(n_q + 2 n_kv)][d], so
+//     the fused QKV projection streams a single contiguous span; the three Tensor structs keep
+//     valid row-major views into it (k and v are marked device_is_view);
+//   * every other tensor has its own 256-byte-aligned allocation;
+//   * one reusable staging buffer carries the BF16 payload to the device (the reference
+//     cudaMallocs and frees a staging buffer per tensor, llama3.cu:203, :234).
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "../csrc/common.cuh"
+#include "../../include/llama3.h"
+#include "../../include/llm_b200_synth.h"
+#include "host_internal.h"
+
+using namespace llmb;
+
+static Tensor *new_tensor() { return static_cast<Tensor *>(calloc(1, sizeof(Tensor))); }
+
+extern "C" Llama3 *init_llama3(int n_layers) {
+    if (n_layers <= 0) return nullptr;
+    Llama3 *m = static_cast<Llama3 *>(calloc(1, sizeof(Llama3)));
+    if (!m) return nullptr;
+    m->n_layers = n_layers;
+    m->embed_tokens = new_tensor();
+    m->norm = new_tensor();
+    m->lm_head = new_tensor();
+    m->layers = static_cast<Llama3Layer **>(calloc((size_t)n_layers, sizeof(Llama3Layer *)));
+    bool ok = m->embed_tokens && m->norm && m->lm_head && m->layers;
+    for (int i = 0; ok && i < n_layers; ++i) {
+        Llama3Layer *l = static_cast<Llama3Layer *>(calloc(1, sizeof(Llama3Layer)));
+        if (!l) { ok = false; break; }
+        l->layernum = i;
+        l->input_layernorm = new_tensor();
+        l->mlp_down_proj = new_tensor();
+        l->mlp_gate_proj = new_tensor();
+        l->mlp_up_proj = new_tensor();
+        l->post_attention_layernorm = new_tensor();
+        l->self_attn_k_proj = new_tensor();
+        l->self_attn_o_proj = new_tensor();
+        l->self_attn_q_proj = new_tensor();
+        l->self_attn_v_proj = new_tensor();
+        m->layers[i] = l;
+        ok = l->input_layernorm && l->mlp_down_proj && l->mlp_gate_proj && l->mlp_up_proj &&
+             l->post_attention_layernorm && l->self_attn_k_proj && l->self_attn_o_proj && l->self_attn_q_proj &&
+             l->self_attn_v_proj;
+    }
+    if (!ok) {
+        free_llama3(m);
+        return nullptr;
+    }
+    // Defaults are the reference's literals; to_cuda fills the shape-derived fields.
+    m->config.head_dim = 128;
+    m->config.max_seq = 2048;
+    m->config.rope_theta = 500000.0f;
+    m->config.eps = 1e-5;
+    m->tp_rank = 0;
+    m->tp_size = 1;
+    return m;
+}
+
+extern "C" void _free_tensor(Tensor *t) {
+    if (!t) return;
+    if (t->d_ndim) cudaFree(t->d_ndim);
+    if (t->d_mem_len) cudaFree(t->d_mem_len);
+    if (t->d_shape) cudaFree(t->d_shape);
+    if (t->d_bf16_tensor) cudaFree(t->d_bf16_tensor);
+    if (t->d_fp16_tensor && !t->device_is_view) cudaFree(t->d_fp16_tensor);
+    free(t->ndim);
+    free(t->mem_len);
+    free(t->shape);
+    free(t->bf16_tensor);
+    free(t);
+}
+
+void llmb::for_each_tensor(Llama3 *m, const std::function<void(Tensor *, int, int)> &fn) {
+    fn(m->embed_tokens, -1, LLMB_SID_EMBED);
+    fn(m->lm_head, -1, LLMB_SID_LM_HEAD);
+    fn(m->norm, -1, LLMB_SID_NORM);
+    for (int i = 0; i < m->n_layers; ++i) {
+        Llama3Layer *l = m->layers[i];
+        if (!l) continue;
+        fn(l->input_layernorm, i, LLMB_SLOT_INPUT_LAYERNORM);
+        fn(l->mlp_down_proj, i, LLMB_SLOT_DOWN);
+        fn(l->mlp_gate_proj, i, LLMB_SLOT_GATE);
+        fn(l->mlp_up_proj, i, LLMB_SLOT_UP);
+        fn(l->post_attention_layernorm, i, LLMB_SLOT_POST_LAYERNORM);
+        fn(l->self_attn_k_proj, i, LLMB_SLOT_K);
+        fn(l->self_attn_o_proj, i, LLMB_SLOT_O);
+        fn(l->self_attn_q_proj, i, LLMB_SLOT_Q);
+        fn(l->self_attn_v_proj, i, LLMB_SLOT_V);
+    }
+}
+
+extern "C" void free_llama3(Llama3 *m) {
+    if (!m) return;
+    if (m->embed_tokens) _free_tensor(m->embed_tokens);
+    if (m->norm) _free_tensor(m->norm);
+    if (m->lm_head) _free_tensor(m->lm_head);
+    if (m->layers) {
+        for (int i = 0; i < m->n_layers; ++i) {
+            Llama3Layer *l = m->layers[i];
+            if (!l) continue;
+            // q owns the fused QKV buffer; k and v are views and must go first or last alike.
+            _free_tensor(l->input_layernorm);
+            _free_tensor(l->mlp_down_proj);
+            _free_tensor(l->mlp_gate_proj);
+            _free_tensor(l->mlp_up_proj);
+            _free_tensor(l->post_attention_layernorm);
+            _free_tensor(l->self_attn_k_proj);
+            _free_tensor(l->self_attn_o_proj);
+            _free_tensor(l->self_attn_q_proj);
+            _free_tensor(l->self_attn_v_proj);
+            free(l);
+        }
+        free(m->layers);
+    }
+    free(m);
+}
+
+extern "C" int llama3_set_config(Llama3 *m, const Llama3Config *c) {
+    if (!m || !c) return LLMB_ERR_INVALID;
+    if (c->d_model > 0) m->config.d_model = c->d_model;
+    if (c->n_q_heads > 0) m->config.n_q_heads = c->n_q_heads;
+    if (c->n_kv_heads > 0) m->config.n_kv_heads = c->n_kv_heads;
+    if (c->head_dim > 0) m->config.head_dim = c->head_dim;
+    if (c->ffn > 0) m->config.ffn = c->ffn;
+    if (c->vocab > 0) m->config.vocab = c->vocab;
+    if (c->max_seq > 0) m->config.max_seq = c->max_seq;
+    if (c->rope_theta > 0.0f) m->config.rope_theta = c->rope_theta;
+    if (c->eps > 0.0) m->config.eps = c->eps;
+    return LLMB_OK;
+}
+
+extern "C" int llama3_set_tp(Llama3 *m, int tp_rank, int tp_size) {
+    if (!m || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return LLMB_ERR_INVALID;
+    if (tp_size != 1) {
+        set_last_error("tensor parallel sharding is not built yet: tp_size must be 1");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    m->tp_rank = tp_rank;
+    m->tp_size = tp_size;
+    return LLMB_OK;
+}
+
+static int set_shape(Tensor *t, int d0, int d1) {
+    free(t->ndim);
+    free(t->mem_len);
+    free(t->shape);
+    int nd = d1 > 0 ? 2 : 1;
+    t->ndim = static_cast<int *>(malloc(sizeof(int)));
+    t->mem_len = static_cast<int *>(malloc(sizeof(int)));
+    t->shape = static_cast<int *>(malloc(sizeof(int) * 2));
+    if (!t->ndim || !t->mem_len || !t->shape) return LLMB_ERR_NOMEM;
+    *t->ndim = nd;
+    t->shape[0] = d0;
+    t->shape[1] = d1 > 0 ? d1 : 1;
+    long long n = (long long)d0 * (d1 > 0 ? d1 : 1);
+    if (n > 0x7fffffffLL) return LLMB_ERR_INVALID;
+    *t->mem_len = (int)n;
+    return LLMB_OK;
+}
+
+// Shape checks + config derivation shared by the file and the synthetic path.
+static int derive_config(Llama3 *m) {
+    Llama3Config &c = m->config;
+    char msg[256];
+    bool missing = false;
+    for_each_tensor(m, [&](Tensor *t, int, int) {
+        if (!t || !t->loaded || !t->shape || !t->ndim) missing = true;
+    });
+    if (missing) {
+        set_last_error("to_cuda: at least one tensor of the model was never loaded");
+        return LLMB_ERR_INVALID;
+    }
+    if (*m->embed_tokens->ndim != 2 || *m->lm_head->ndim != 2) {
+        set_last_error("to_cuda: embed_tokens and lm_head must be 2-D");
+        return LLMB_ERR_INVALID;
+    }
+    c.d_model = m->embed_tokens->shape[1];
+    c.vocab = m->lm_head->shape[0];
+    const Llama3Layer *l0 = m->layers[0];
+    c.ffn = l0->mlp_gate_proj->shape[0];
+    const int q_rows = l0->self_attn_q_proj->shape[0], kv_rows = l0->self_attn_k_proj->shape[0];
+    if (c.head_dim <= 0 || q_rows % c.head_dim || kv_rows % c.head_dim) {
+        snprintf(msg, sizeof msg, "to_cuda: q rows %d / kv rows %d are not multiples of head_dim %d", q_rows, kv_rows,
+                 c.head_dim);
+        set_last_error(msg);
+        return LLMB_ERR_INVALID;
+    }
+    c.n_q_heads = q_rows / c.head_dim;
+    c.n_kv_heads = kv_rows / c.head_dim;
+    if (c.n_kv_heads <= 0 || c.n_q_heads % c.n_kv_heads) {
+        set_last_error("to_cuda: query heads are not a multiple of KV heads");
+        return LLMB_ERR_INVALID;
+    }
+    auto is = [](const Tensor *t, int d0, int d1) {
+        return d1 > 0 ? (*t->ndim == 2 && t->shape[0] == d0 && t->shape[1] == d1) : (*t->ndim == 1 && t->shape[0] == d0);
+    };
+    bool ok = is(m->lm_head, c.vocab, c.d_model) && is(m->norm, c.d_model, 0) && m->embed_tokens->shape[0] > 0;
+    for (int i = 0; ok && i < m->n_layers; ++i) {
+        const Llama3Layer *l = m->layers[i];
+        ok = is(l->input_layernorm, c.d_model, 0) && is(l->post_attention_layernorm, c.d_model, 0) &&
+             is(l->self_attn_q_proj, q_rows, c.d_model) && is(l->self_attn_k_proj, kv_rows, c.d_model) &&
+             is(l->self_attn_v_proj, kv_rows, c.d_model) && is(l->self_attn_o_proj, c.d_model, q_rows) &&
+             is(l->mlp_gate_proj, c.ffn, c.d_model) && is(l->mlp_up_proj, c.ffn, c.d_model) &&
+             is(l->mlp_down_proj, c.d_model, c.ffn);
+    }
+    if (!ok) {
+        set_last_error("to_cuda: tensor shapes are inconsistent with a LLaMA3 decoder");
+        return LLMB_ERR_INVALID;
+    }
+    if (c.d_model % 8 || c.ffn % 8 || (c.head_dim != 64 && c.head_dim != 128)) {
+        set_last_error("to_cuda: d_model and ffn must be multiples of 8 and head_dim 64 or 128");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    m->config_ready = 1;
+    return LLMB_OK;
+}
+
+// Destination of each tensor on the device; allocates own buffers and the fused QKV buffer.
+static int place_tensors(Llama3 *m) {
+    const Llama3Config &c = m->config;
+    auto own = [](Tensor *t) -> int {
+        void *p = nullptr;
+        LLMB_CUDA_OK(cudaMalloc(&p, (size_t)(*t->mem_len) * 2));
+        t->d_fp16_tensor = static_cast<llmb_half *>(p);
+        t->device_is_view = 0;
+        return LLMB_OK;
+    };
+    int rc;
+    if ((rc = own(m->embed_tokens)) || (rc = own(m->lm_head)) || (rc = own(m->norm))) return rc;
+    const size_t q_elems = (size_t)c.n_q_heads * c.head_dim * c.d_model;
+    const size_t kv_elems = (size_t)c.n_kv_heads * c.head_dim * c.d_model;
+    for (int i = 0; i < m->n_layers; ++i) {
+        Llama3Layer *l = m->layers[i];
+        if ((rc = own(l->input_layernorm)) || (rc = own(l->post_attention_layernorm)) ||
+            (rc = own(l->self_attn_o_proj)) || (rc = own(l->mlp_gate_proj)) || (rc = own(l->mlp_up_proj)) ||
+            (rc = own(l->mlp_down_proj)))
+            return rc;
+        void *qkv = nullptr;
+        LLMB_CUDA_OK(cudaMalloc(&qkv, (q_elems + 2 * kv_elems) * 2));
+        llmb_half *base = static_cast<llmb_half *>(qkv);
+        l->self_attn_q_proj->d_fp16_tensor = base;
+        l->self_attn_q_proj->device_is_view = 0;  // owner of the fused buffer
+        l->self_attn_k_proj->d_fp16_tensor = base + q_elems;
+        l->self_attn_k_proj->device_is_view = 1;
+        l->self_attn_v_proj->d_fp16_tensor = base + q_elems + kv_elems;
+        l->self_attn_v_proj->device_is_view = 1;
+    }
+    return LLMB_OK;
+}
+
+extern "C" int llama3_to_cuda(Llama3 *m) {
+    if (!m) return LLMB_ERR_INVALID;
+    int rc = derive_config(m);
+    if (rc) return rc;
+    if ((rc = place_tensors(m))) return rc;
+    size_t max_elems = 0;
+    for_each_tensor(m, [&](Tensor *t, int, int) {
+        if ((size_t)*t->mem_len > max_elems) max_elems = (size_t)*t->mem_len;
+    });
+    void *staging = nullptr;
+    LLMB_CUDA_OK(cudaMalloc(&staging, max_elems * 2));
+    int status = LLMB_OK;
+    for_each_tensor(m, [&](Tensor *t, int, int) {
+        if (status) return;
+        if (!t->bf16_tensor) {
+            set_last_error("to_cuda: tensor payload missing on the host");
+            status = LLMB_ERR_INVALID;
+            return;
+        }
+        const size_t n = (size_t)*t->mem_len;
+        cudaError_t e;
+        if (t->file_dtype == 1) {  // F16 file: pass through
+            e = cudaMemcpy(t->d_fp16_tensor, t->bf16_tensor, n * 2, cudaMemcpyHostToDevice);
+        } else {
+            e = cudaMemcpy(staging, t->bf16_tensor, n * 2, cudaMemcpyHostToDevice);
+            if (e == cudaSuccess) {
+                int r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(staging),
+                                          reinterpret_cast<uint16_t *>(t->d_fp16_tensor), n, nullptr);
+                if (r) status = r;
+                if (!r) e = cudaDeviceSynchronize();  // staging is reused by the next tensor
+            }
+        }
+        if (e != cudaSuccess && !status) status = cuda_fail(e, __FILE__, __LINE__);
+        free(t->bf16_tensor);  // llama3.cu:211
+        t->bf16_tensor = nullptr;
+    });
+    cudaFree(staging);
+    return status;
+}
+
+extern "C" void to_cuda(Llama3 *m) {
+    int rc = llama3_to_cuda(m);
+    if (rc) {
+        printf("Error: to_cuda failed (%d): %s\n", rc, llmb_last_error());
+        exit(1);
+    }
+}
+
+extern "C" int llama3_synth_weights(Llama3 *m, const Llama3Config *cfg, uint64_t seed, int bf16) {
+    if (!m || !cfg) return LLMB_ERR_INVALID;
+    if (cfg->d_model <= 0 || cfg->n_q_heads <= 0 || cfg->n_kv_heads <= 0 || cfg->head_dim <= 0 || cfg->ffn <= 0 ||
+        cfg->vocab <= 0)
+        return LLMB_ERR_INVALID;
+    int rc = llama3_set_config(m, cfg);
+    if (rc) return rc;
+    const Llama3Config &c = m->config;
+    const int q_rows = c.n_q_heads * c.head_dim, kv_rows = c.n_kv_heads * c.head_dim;
+    auto shape = [&](Tensor *t, int d0, int d1) {
+        int r = set_shape(t, d0, d1);
+        t->loaded = 1;
+        t->file_dtype = bf16 ? 0 : 1;
+        return r;
+    };
+    rc = shape(m->embed_tokens, c.vocab, c.d_model) | shape(m->lm_head, c.vocab, c.d_model) | shape(m->norm, c.d_model, 0);
+    for (int i = 0; i < m->n_layers; ++i) {
+        Llama3Layer *l = m->layers[i];
+        rc |= shape(l->input_layernorm, c.d_model, 0) | shape(l->post_attention_layernorm, c.d_model, 0) |
+              shape(l->self_attn_q_proj, q_rows, c.d_model) | shape(l->self_attn_k_proj, kv_rows, c.d_model) |
+              shape(l->self_attn_v_proj, kv_rows, c.d_model) | shape(l->self_attn_o_proj, c.d_model, q_rows) |
+              shape(l->mlp_gate_proj, c.ffn, c.d_model) | shape(l->mlp_up_proj, c.ffn, c.d_model) |
+              shape(l->mlp_down_proj, c.d_model, c.ffn);
+    }
+    if (rc) return LLMB_ERR_INVALID;
+    if ((rc = derive_config(m))) return rc;
+    if ((rc = place_tensors(m))) return rc;
+    size_t max_elems = 0;
+    for_each_tensor(m, [&](Tensor *t, int, int) {
+        if ((size_t)*t->mem_len > max_elems) max_elems = (size_t)*t->mem_len;
+    });
+    void *staging = nullptr;
+    if (bf16) LLMB_CUDA_OK(cudaMalloc(&staging, max_elems * 2));
+    int status = LLMB_OK;
+    for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
+        if (status) return;
+        const uint64_t n = (uint64_t)*t->mem_len;
+        const bool is_norm = (layer < 0 && slot == LLMB_SID_NORM) ||
+                             (layer >= 0 && (slot == LLMB_SLOT_INPUT_LAYERNORM || slot == LLMB_SLOT_POST_LAYERNORM));
+        const uint64_t sid = layer < 0 ? (uint64_t)slot : LLMB_LAYER_SID(layer, slot);
+        uint16_t *dst = reinterpret_cast<uint16_t *>(t->d_fp16_tensor);
+        int r;
+        if (is_norm) {
+            r = llmb_fill_u16(dst, 0x3C00, n, nullptr);  // gain 1.0
+        } else if (bf16) {
+            r = llmb_synth_bf16(static_cast<uint16_t *>(staging), seed, sid, 0.02f, 0, n, nullptr);
+            if (!r) r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(staging), dst, n, nullptr);
+        } else {
+            r = llmb_synth_fp16(dst, seed, sid, 0.02f, 0, n, nullptr);
+        }
+        if (r) status = r;
+    });
+    cudaError_t e = cudaDeviceSynchronize();
+    if (staging) cudaFree(staging);
+    if (!status && e != cudaSuccess) status = cuda_fail(e, __FILE__, __LINE__);
+    return status;
+}
