@@ -269,7 +269,7 @@ def run_reference(args):
         if r.returncode != 0:
             print(json.dumps(dict(base, unavailable="reference harness exited %d: %s" % (r.returncode, r.stderr[-200:]))))
             return
-        info = json.loads(r.stdout.strip().splitlines()[-1])
+        info = json.loads(r.stdout[r.stdout.rindex('{"n_layers"'):])  # the reference prints ANSI colour codes before it
     secs = info["step_s"][warm:]
     total = sum(secs)
     val = len(secs) / total
@@ -288,6 +288,7 @@ def run_reference(args):
 
 
 def main():
+    global PROMPT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -297,7 +298,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-max-steps", type=int, default=6)
     ap.add_argument("--tmpdir", default=None)
+    ap.add_argument("--prompt-len", type=int, default=PROMPT, help="shorter prompts are for profiling runs only")
     args = ap.parse_args()
+    PROMPT = args.prompt_len
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -70,7 +70,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Every wait in these kernels is bounded.  try_wait suspends for a hardware-defined time slice
 // per call, so the cap below is on the order of seconds; a wait that runs out records `code`
 // in the status word and returns false, and the caller winds the kernel down.
-constexpr uint32_t kWaitSpins = 1u << 24;
+constexpr uint32_t kWaitSpins = 1u << 20;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
     for (uint32_t i = 0; i < kWaitSpins; ++i)

@@ -189,7 +189,7 @@ int run_step(Engine *e, bool with_logits, int len) {
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
         cudaGraph_t graph = nullptr;
-        LLMB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        LLMB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
         int rc = enqueue_step(e, with_logits, sp);
         cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
         if (rc) {
@@ -269,6 +269,7 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
     };
     if (!m || !m->config_ready) return fail(LLMB_ERR_INVALID, "init_cache: call to_cuda first");
     const Llama3Config &c = m->config;
+    if (!device_status_ptr()) return fail(LLMB_ERR_CUDA, "init_cache: could not allocate the device status word");
     Engine *e = new Engine();
     e->model = m;
     e->d = c.d_model;

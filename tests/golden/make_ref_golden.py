@@ -43,7 +43,7 @@ def main():
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.exit("reference harness failed (%d): %s" % (r.returncode, r.stderr[-500:]))
-        info = json.loads(r.stdout.strip().splitlines()[-1])
+        info = json.loads(r.stdout[r.stdout.rindex('{"n_layers"'):])  # the reference prints ANSI colour codes before it
         logits = np.fromfile(logit_path, dtype=np.uint16).reshape(N_STEPS, cfg.vocab)
     vals = logits.view(np.float16).astype(np.float32)
     order = np.argsort(-vals, axis=1, kind="stable")[:, :TOPK]
