@@ -143,6 +143,10 @@ int cache_reset(CudaCache *cache);
  * (programmatic dependent launch between kernels, default 1), copy_logits (device->host copy
  * of the logits on every call, default 1). Negative value = leave unchanged. */
 int cache_set_options(CudaCache *cache, int use_graph, int use_pdl, int copy_logits);
+/* Chooses between the two decode paths: 1 (default where the device allows a cooperative launch)
+ * = one persistent kernel per token (llmb_decode_step); 0 = one kernel per fused operation,
+ * captured into a CUDA graph (llmb_gemv_f16, llmb_attn_decode, ...). */
+int cache_use_step_kernel(CudaCache *cache, int enable);
 /* When enabled, every decode step also copies the residual stream after the embedding and
  * after each layer into an [n_layers + 1][d_model] FP16 device buffer (disables the graph). */
 int cache_enable_hidden_dump(CudaCache *cache, int enable);

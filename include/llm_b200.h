@@ -150,6 +150,56 @@ int llmb_argmax_f16(const uint16_t *d_logits, int n, int32_t *d_token_out, int32
 /* position += 1 without sampling (prompt rows whose logits nobody reads). */
 int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
 
+/* ------------------------------------------------------------------------------------ */
+/* One whole decode step as a single persistent kernel: every phase of the reference's     */
+/* inference() loop body (inference.cu:149-193) for one new row -- embedding row, per layer */
+/* RMSNorm + QKV + RoPE + cache append, attention over the cache, o_proj + residual,        */
+/* RMSNorm + SwiGLU FFN + residual, then final norm, lm_head and greedy argmax -- with the  */
+/* weights of all projections streamed through one shared-memory ring across the phase      */
+/* boundaries.  One CTA per SM, cooperative launch.  Same arithmetic and rounding points as  */
+/* llmb_gemv_f16 / llmb_attn_decode.                                                        */
+/*   history[pos] is the input token; with_logits != 0: logits[vocab], next_token[0] and     */
+/*   history[pos + 1] are written; pos is advanced by one.                                   */
+/*   scratch: llmb_decode_step_scratch_bytes() bytes, 256-byte aligned, zeroed once before   */
+/*   the first launch and whenever llmb_device_status() reports a non-zero status.           */
+/*   split_len must be a multiple of 64; n_splits * split_len >= pos + 1.                    */
+/* ------------------------------------------------------------------------------------ */
+typedef struct {
+    const uint16_t *wqkv;   /* [(n_q + 2 n_kv)][d_model]: q, k, v rows back to back */
+    const uint16_t *wo;     /* [d_model][n_q] */
+    const uint16_t *wgate;  /* [ffn][d_model] */
+    const uint16_t *wup;    /* [ffn][d_model] */
+    const uint16_t *wdown;  /* [d_model][ffn] */
+    const uint16_t *g_in;   /* input_layernorm gain [d_model] */
+    const uint16_t *g_post; /* post_attention_layernorm gain [d_model] */
+    uint16_t *k_cache;      /* [max_pos][n_kv] */
+    uint16_t *v_cache;
+} LlmbLayer;
+
+typedef struct {
+    const LlmbLayer *layers; /* device array [n_layers] */
+    int n_layers, d_model, n_q_heads, n_kv_heads, head_dim, ffn, vocab, embed_rows, max_pos;
+    float rope_theta;
+    double eps;
+    const uint16_t *embed, *lm_head, *g_final;
+    const int32_t *history; /* device: token ids by position; history[pos + 1] is written */
+    int history_len;
+    int32_t *pos;           /* device: rows already in the cache = position of this token */
+    uint16_t *x, *q, *attn, *h, *logits; /* [d_model], [n_q], [n_q], [ffn], [vocab] */
+    int32_t *next_token;
+    void *scratch;
+    int max_splits;         /* the value scratch was sized for */
+    int n_splits, split_len;
+    int with_logits;
+    uint16_t *hidden;       /* optional [n_layers + 1][d_model]: residual stream after each layer */
+    uint64_t *trace;        /* optional profiling aid, device [4][5 * n_layers + 2][4] nanosecond stamps:
+                               CTAs 0, 1, middle, last; per phase: entered, dependency met, input ready,
+                               done.  NULL in production. */
+} LlmbDecodeStepArgs;
+
+size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits);
+int llmb_decode_step(const LlmbDecodeStepArgs *args, llmb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

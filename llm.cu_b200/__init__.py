@@ -24,13 +24,13 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_argmax_f16", "llmb_advance_pos",
+    "llmb_attn_decode", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
     "llama3_to_cuda", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
-    "cache_set_options", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue",
+    "cache_set_options", "cache_use_step_kernel", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue",
     "cache_kernel_launches",
 ]
 
@@ -136,7 +136,11 @@ def _declare(l):
     l.free_cache.restype = None
     l.cache_reset.argtypes = [K]
     l.cache_set_options.argtypes = [K, i32, i32, i32]
+    l.cache_use_step_kernel.argtypes = [K, i32]
     l.cache_enable_hidden_dump.argtypes = [K, i32]
+    l.llmb_decode_step_scratch_bytes.argtypes = [i32, i32, i32, i32]
+    l.llmb_decode_step_scratch_bytes.restype = sz
+    l.llmb_decode_step.argtypes = [vp, vp]
     l.cache_read_hidden.argtypes = [K, vp]
     l.inference_greedy.argtypes = [M, K, C.POINTER(C.c_int), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_float),
                                    C.POINTER(C.c_float)]

@@ -16,12 +16,14 @@ SOURCES = [
     "csrc/misc.cu",
     "csrc/gemv.cu",
     "csrc/attn_decode.cu",
+    "csrc/decode_step.cu",
     "host/model.cu",
     "host/engine.cu",
     "host/safetensor.cpp",
 ]
 HEADERS = [
     "csrc/common.cuh",
+    "csrc/gemv_common.cuh",
     "host/host_internal.h",
     "../include/llm_b200.h",
     "../include/llama3.h",

@@ -79,6 +79,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
     return false;
 }
 
+// Warp-collective wait: every lane tries once (the common case: the data is already there); if not,
+// lane 0 alone polls, so a waiting CTA does not flood the shared-memory pipe that the bulk copies
+// need to land their data, and the other lanes take one more try_wait afterwards to acquire the
+// phase themselves.  All 32 lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *status, int code, int lane) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok && lane != 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;  // already complete: returns at once
+    return ok != 0;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Source,
 // destination and size must be multiples of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar,

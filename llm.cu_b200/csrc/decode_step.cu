@@ -1,0 +1,743 @@
+// One decode step of the whole model as ONE persistent kernel (one CTA per SM, cooperative
+// launch): the per-token forward loop of the reference (inference.cu:149-193) for a single new
+// row, without a kernel boundary between its phases.
+//
+// Why: at batch 1 a layer is five dependent phases of 5-36 us each.  As separate kernels each
+// boundary drains and refills the memory pipeline; here a producer thread streams the weights of
+// every projection, in program order, through one shared-memory ring with 1-D bulk copies and
+// runs ahead of the math across phase boundaries, so HBM keeps working while the CTAs
+// synchronise.  The phases are the fused operations of gemv.cu / attn_decode.cu:
+//
+//   per layer   QKV    RMSNorm(x) -> [q;k;v] rows -> RoPE -> q buffer / KV-cache row `pos`
+//               ATTN   split-KV softmax(q K^T / sqrt(hd)) V, last CTA per KV head merges
+//               O      o_proj + residual add into x
+//               GU     RMSNorm(x) -> SiLU(gate) * up -> h
+//               DOWN   down_proj + residual add into x
+//   then        LM     RMSNorm(x) -> FP16 logits, per-CTA argmax; CTA 0 picks the first maximum,
+//                      appends it to the history and advances `pos`
+//
+// Bound: HBM.  Algorithmic bytes per launch = all projection weights + lm_head + norm gains + one
+// embedding row + (pos + 1) KV rows read + one KV row written.
+//
+// Synchronisation: a monotonically increasing 64-bit arrival counter in global memory; phase p of
+// a launch waits for base + (p + 1) * gridDim.x, and CTA 0 stores the next launch's base at the
+// end.  Every wait (mbarrier or counter) is bounded: on expiry the CTA records a status code,
+// stops waiting for anything else and runs to the end without touching the ring.
+#include <cstdlib>
+
+#include "gemv_common.cuh"
+
+namespace llmb {
+
+constexpr int kDsWarps = 16;                  // consumer warps
+constexpr int kDsConsumers = kDsWarps * 32;   // 512
+constexpr int kDsThreads = kDsConsumers;      // no dedicated producer: 4 warps per scheduler at 128 registers
+constexpr int kDsGroups = 2;                  // consumer groups; group g owns ring stages with it % 2 == g
+constexpr int kDsGWarps = kDsWarps / kDsGroups;   // 8
+constexpr int kDsGThreads = kDsGWarps * 32;       // 256
+constexpr int kDsSlots = 6;
+constexpr uint32_t kDsSlotBytes = 32 * 1024;
+constexpr int kDsJ = 8;                       // 16-byte chunks of x per thread: k <= 16384
+constexpr int kDsTile = 32;                   // cache rows per attention tile
+constexpr uint32_t kPollLimit = 1u << 22;
+
+struct DsLayer {
+    const __half *wqkv, *wo, *wgate, *wup, *wdown, *g_in, *g_post;
+    __half *k_cache, *v_cache;
+};
+
+struct DsParams {
+    const DsLayer *layers;
+    const __half *embed, *lm_head, *g_final;
+    const int *history;
+    int *pos;
+    __half *x, *q, *attn, *h, *logits, *hidden;
+    int *next_token;
+    unsigned long long *bar;  // [0] arrival counter, [1] base of the next launch
+    int *attn_counters;       // [n_kv_heads]
+    float *part_ml, *part_o;  // attention partials
+    float *amax_val;          // [gridDim]
+    int *amax_idx;
+    int *status;
+    unsigned long long *trace;  // optional: [4 CTAs][phases][4] globaltimer stamps
+    double eps;
+    float rope_theta;
+    int n_layers, d, nq, nkv, hd, ffn, vocab, embed_rows, max_pos;
+    int n_splits, split_len, with_logits, history_len;
+};
+
+enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
+
+struct GemvDesc {
+    const __half *w, *w2, *x, *gamma, *res;
+    __half *y, *hidden_row;
+    int n, k, nr, R, kind;
+};
+
+__device__ __forceinline__ int rows_per_stage(int k) {
+    const int fit = (int)(kDsSlotBytes / (uint32_t)(k * 2));
+    return fit >= 8 ? 8 : (fit >= 4 ? 4 : (fit >= 2 ? 2 : 1));
+}
+
+// Projection `kind` of layer `l` (l ignored for PH_LM).  `emb` is the embedding row of this step.
+__device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, int l, int kind, const __half *emb) {
+    GemvDesc g;
+    g.kind = kind;
+    g.w2 = nullptr;
+    g.gamma = nullptr;
+    g.res = nullptr;
+    g.hidden_row = nullptr;
+    const int nq = p.nq * p.hd, nkv = p.nkv * p.hd;
+    if (kind == PH_LM) {
+        g.w = p.lm_head; g.x = p.x; g.gamma = p.g_final; g.y = p.logits; g.n = p.vocab; g.k = p.d;
+    } else {
+        const DsLayer &L = p.layers[l];
+        if (kind == PH_QKV) {
+            g.w = L.wqkv; g.x = (l == 0) ? emb : p.x; g.gamma = L.g_in; g.y = p.q; g.n = nq + 2 * nkv; g.k = p.d;
+        } else if (kind == PH_O) {
+            g.w = L.wo; g.x = p.attn; g.res = (l == 0) ? emb : p.x; g.y = p.x; g.n = p.d; g.k = nq;
+        } else if (kind == PH_GU) {
+            g.w = L.wgate; g.w2 = L.wup; g.x = p.x; g.gamma = L.g_post; g.y = p.h; g.n = p.ffn; g.k = p.d;
+        } else {
+            g.w = L.wdown; g.x = p.h; g.res = p.x; g.y = p.x; g.n = p.d; g.k = p.ffn;
+            if (p.hidden) g.hidden_row = p.hidden + (size_t)(l + 1) * p.d;
+        }
+    }
+    g.nr = rows_per_stage(g.k);
+    g.R = (kind == PH_GU) ? g.nr / 2 : g.nr;
+    return g;
+}
+
+__device__ __forceinline__ void cta_range(int groups, int &begin, int &end) {
+    begin = (int)(((long long)groups * blockIdx.x) / gridDim.x);
+    end = (int)(((long long)groups * (blockIdx.x + 1)) / gridDim.x);
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void cp_async16_ds(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all_ds() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Where a consumer group's weight stream stands: the next ring stage to request.
+struct DsCursor {
+    const unsigned char *w, *w2;
+    size_t row_bytes;
+    int ph, rg, rg_end, n, R;
+    uint32_t it;
+};
+
+struct DsShared {
+    uint64_t full_bar[kDsSlots];
+    DsCursor cur[kDsGroups];
+    float red[kDsGroups][2][8][kDsGWarps];
+    float norm_buf[kDsGroups][512];
+    float2 rope_cs[64];
+    float q_s[8 * 128];
+    float p_s[8 * kDsTile];
+    float scale_s[8];
+    float m_s[8], l_s[8];
+    float norm_rms[kDsGroups];
+    float best_val[kDsGroups];
+    int best_idx[kDsGroups];
+    int abort_flag;
+    int is_last;
+};
+
+// Requests the next ring stage that belongs to consumer group `grp` (stages alternate between the
+// groups), walking on through the projections in program order.  Called by one thread of the group
+// right after the group has finished with the slot that stage maps to.
+__device__ __noinline__ void issue_next_stage(const DsParams &p, const __half *emb, DsCursor &c, int grp, int n_gemv,
+                                              unsigned char *ring, uint64_t *full_bar) {
+    for (;;) {
+        if (c.ph >= n_gemv) return;
+        if (c.rg >= c.rg_end) {
+            if (++c.ph >= n_gemv) return;
+            const GemvDesc g = gemv_desc(p, c.ph >> 2, (c.ph < 4 * p.n_layers) ? (c.ph & 3) : PH_LM, emb);
+            c.w = reinterpret_cast<const unsigned char *>(g.w);
+            c.w2 = reinterpret_cast<const unsigned char *>(g.w2);
+            c.row_bytes = (size_t)g.k * 2;
+            c.n = g.n;
+            c.R = g.R;
+            cta_range((g.n + g.R - 1) / g.R, c.rg, c.rg_end);
+            continue;
+        }
+        const uint32_t it = c.it++;
+        const int rg = c.rg++;
+        if ((int)(it % kDsGroups) != grp) continue;
+        const int s = it % kDsSlots;
+        const int row0 = rg * c.R;
+        const int rows = min(c.R, c.n - row0);
+        unsigned char *dst = ring + (size_t)s * kDsSlotBytes;
+        const uint32_t bytes = (uint32_t)(rows * c.row_bytes);
+        const uint64_t policy = policy_evict_first();
+        fence_proxy_async();  // the slot was last read through the generic proxy
+        mbar_arrive_expect_tx(&full_bar[s], c.w2 ? 2 * bytes : bytes);
+        bulk_g2s(dst, c.w + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
+        if (c.w2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, c.w2 + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
+        return;
+    }
+}
+
+template <int NR>
+__device__ __forceinline__ float stage_dot(const unsigned char *base, size_t row_bytes, int rows, bool dual,
+                                           const uint4 (&xh)[kDsJ], const bool (&have)[kDsJ], int gtid, int lane) {
+    // NR rows fit a 32 KB stage only if a row has at most 8 / NR chunks per thread, so the chunk loop
+    // is bounded by NJ and no issue slot goes to chunks that cannot exist.
+    constexpr int NJ = kDsJ / NR;
+    uint4 xs[NJ];
+    bool hs[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        xs[j] = xh[j];
+        hs[j] = have[j];
+    }
+    float acc[NR];
+    if (dual) stage_dot_rows<NR, NJ, true>(base, row_bytes, rows, gtid, kDsGThreads, xs, hs, acc);
+    else stage_dot_rows<NR, NJ, false>(base, row_bytes, rows, gtid, kDsGThreads, xs, hs, acc);
+    return warp_reduce_multi<NR>(acc, lane);
+}
+
+__global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsParams p) {
+    extern __shared__ __align__(128) unsigned char ds_smem[];
+    unsigned char *ring = ds_smem;
+    __half *k_tile = reinterpret_cast<__half *>(ds_smem + (size_t)kDsSlots * kDsSlotBytes);
+    __half *v_tile = k_tile + kDsTile * 128;
+    __shared__ DsShared sh;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kDsSlots; ++s) {
+            mbar_init(&sh.full_bar[s], 1);
+        }
+        fence_mbar_init();
+        sh.abort_flag = 0;
+        for (int g = 0; g < kDsGroups; ++g) {
+            sh.best_val[g] = -INFINITY;
+            sh.best_idx[g] = 0x7fffffff;
+        }
+    }
+    __syncthreads();
+
+    const int pos = *p.pos;
+    int tok = p.history[pos];
+    tok = tok < 0 ? 0 : (tok >= p.embed_rows ? p.embed_rows - 1 : tok);
+    const __half *emb = p.embed + (size_t)tok * p.d;
+    const int n_gemv = 4 * p.n_layers + (p.with_logits ? 1 : 0);
+
+    const int grp = warp / kDsGWarps;   // consumer group of this warp
+    const int gwarp = warp % kDsGWarps;  // warp index inside the group
+    const int gtid = tid % kDsGThreads;  // thread index inside the group
+    // Start the weight stream: each group requests its first kDsSlots / 2 stages.
+    if (gtid == 0) {
+        DsCursor &c = sh.cur[grp];
+        c.ph = -1;
+        c.rg = c.rg_end = 0;
+        c.it = 0;
+        for (int k = 0; k < kDsSlots / kDsGroups; ++k) issue_next_stage(p, emb, c, grp, n_gemv, ring, sh.full_bar);
+    }
+    // RoPE angles of this position (inference.cu:673-678), once per CTA.
+    if (tid < p.hd / 2) {
+        const float freq = 1.0f / powf(p.rope_theta, 2.0f * (float)tid / (float)p.hd);
+        const float angle = (float)pos * freq;
+        sh.rope_cs[tid] = make_float2(cosf(angle), sinf(angle));
+    }
+    if (p.hidden && blockIdx.x == 0)
+        for (int i = tid; i < p.d; i += kDsConsumers) p.hidden[i] = emb[i];
+
+    const unsigned long long bar_base = p.bar[1];
+    unsigned long long n_bar = 0;  // barriers passed in this launch
+    bool ok = true;
+    uint32_t it = 0;
+
+    // arrive: every global write of this CTA for the finished phase is ordered before the count
+    auto grid_arrive = [&]() {
+        named_bar_sync(3, kDsConsumers);
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(p.bar, 1ULL);
+        }
+    };
+    auto grid_wait = [&]() {
+        ++n_bar;
+        if (tid == 0 && ok) {
+            const unsigned long long target = bar_base + n_bar * (unsigned long long)gridDim.x;
+            uint32_t polls = 0;
+            while (ld_acquire_u64(p.bar) < target) {
+                if (++polls > kPollLimit) {
+                    atomicExch(p.status, 202);
+                    sh.abort_flag = 1;
+                    break;
+                }
+            }
+        }
+        named_bar_sync(3, kDsConsumers);
+        if (sh.abort_flag) ok = false;
+    };
+
+    const int n_q = p.nq * p.hd, n_kv = p.nkv * p.hd;
+    const int G = p.nq / p.nkv;
+    // profiling aid: CTAs 0, 1, mid and last stamp the global timer four times per phase
+    int trace_row = -1;
+    if (p.trace && tid == 0) {
+        const int b = blockIdx.x, gdim = gridDim.x;
+        trace_row = b == 0 ? 0 : (b == 1 ? 1 : (b == gdim / 2 ? 2 : (b == gdim - 1 ? 3 : -1)));
+    }
+    auto stamp = [&](int phase, int which) {
+        if (trace_row >= 0) p.trace[((size_t)trace_row * (5 * p.n_layers + 2) + phase) * 4 + which] = globaltimer_ns();
+    };
+    int tphase = 0;
+
+    int gi = 0;                          // stages this group has processed (red double buffer)
+
+    for (int ph = 0; ph <= 4 * p.n_layers; ++ph) {
+        const bool is_lm = ph == 4 * p.n_layers;
+        if (is_lm && !p.with_logits) break;
+        const int l = ph >> 2;
+        const GemvDesc g = gemv_desc(p, l, is_lm ? PH_LM : (ph & 3), emb);
+        const int nchunks = g.k >> 3;
+        const size_t row_bytes = (size_t)g.k * 2;
+        bool have[kDsJ];
+#pragma unroll
+        for (int j = 0; j < kDsJ; ++j) have[j] = (gtid + kDsGThreads * j) < nchunks;
+        stamp(tphase, 0);
+        if (g.gamma) {  // the gain vector does not depend on the previous phase: bring it to L2 now
+#pragma unroll
+            for (int j = 0; j < kDsJ; ++j)
+                if (have[j] && grp == 0)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4 *>(g.gamma) + gtid + kDsGThreads * j));
+        }
+        if (ph > 0) grid_wait();  // the phase that produced x has finished everywhere
+        stamp(tphase, 1);
+
+        // Both groups hold the whole input row in registers (packed FP16): thread t of a group owns
+        // the 16-byte chunks t, t + 256, ...
+        constexpr int kNormJ = kDsJ / 2;  // normalised inputs have k = d_model <= 8192
+        uint4 xh[kDsJ];
+        uint4 gv[kNormJ];
+#pragma unroll
+        for (int j = 0; j < kDsJ; ++j)
+            xh[j] = have[j] ? __ldcg(reinterpret_cast<const uint4 *>(g.x) + gtid + kDsGThreads * j) : make_uint4(0, 0, 0, 0);
+        if (g.gamma) {
+#pragma unroll
+            for (int j = 0; j < kNormJ; ++j)
+                gv[j] = have[j] ? __ldg(reinterpret_cast<const uint4 *>(g.gamma) + gtid + kDsGThreads * j)
+                                : make_uint4(0, 0, 0, 0);
+        }
+        if (g.gamma) {
+            // Sum of squares in the reference's reduction order (inference.cu:309-344): a partial per
+            // four consecutive elements, then a binary tree with offsets halving from (k/4)/2.  Chunk
+            // c = t + 256 j holds partials 2c, 2c+1: offsets >= 512 stay inside a thread, 256..64 cross
+            // warps (shared memory), 32..2 are shuffles, the last is inside a thread again.
+            float p0[kNormJ], p1[kNormJ];
+#pragma unroll
+            for (int j = 0; j < kNormJ; ++j) sumsq_partials(xh[j], p0[j], p1[j]);
+#pragma unroll
+            for (int off = kNormJ / 2; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int j = 0; j < off; ++j) {
+                    p0[j] += p0[j + off];
+                    p1[j] += p1[j + off];
+                }
+            }
+            float *nb = sh.norm_buf[grp];
+            nb[2 * gtid] = p0[0];
+            nb[2 * gtid + 1] = p1[0];
+            named_bar_sync(6 + grp, kDsGThreads);
+            if (gwarp == 0) {
+                float v[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float *b = nb + 2 * lane + e;
+                    v[e] = ((b[0] + b[256]) + (b[128] + b[384])) + ((b[64] + b[320]) + (b[192] + b[448]));
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    v[0] += __shfl_down_sync(0xffffffffu, v[0], off);
+                    v[1] += __shfl_down_sync(0xffffffffu, v[1], off);
+                }
+                if (lane == 0) sh.norm_rms[grp] = sqrtf((float)(p.eps + (double)((v[0] + v[1]) / (float)g.k)));
+            }
+            named_bar_sync(6 + grp, kDsGThreads);
+            const float rms = sh.norm_rms[grp];
+#pragma unroll
+            for (int j = 0; j < kNormJ; ++j)
+                if (have[j]) xh[j] = rmsnorm_apply8(xh[j], gv[j], rms);  // (0 * g) / rms would hit the division's slow path
+        }
+        stamp(tphase, 2);
+
+        // ---- stream this CTA's row groups: ring stage `it` belongs to consumer group it % 2 ----
+        int gb, ge;
+        cta_range((g.n + g.R - 1) / g.R, gb, ge);
+        const bool dual = g.w2 != nullptr;
+        for (int rg = gb; rg < ge; ++rg, ++it) {
+            if ((int)(it % kDsGroups) != grp) continue;
+            const int s = it % kDsSlots;
+            const int i = gi++;
+            // `ok` only changes right after a barrier of the whole group, so that every thread of the
+            // group takes the same path through the barriers below even when a wait gives up.
+            bool got = false;
+            if (ok) {
+                got = mbar_wait_warp(&sh.full_bar[s], (it / kDsSlots) & 1, p.status, 203, lane);
+                if (!got) sh.abort_flag = 1;
+            }
+            const int row0 = rg * g.R;
+            const int rows = min(g.R, g.n - row0);
+            const unsigned char *base = ring + (size_t)s * kDsSlotBytes;
+            float tot = 0.0f;
+            int my_row = 0;
+            if (got) {
+                switch (g.nr) {
+                    case 8: tot = stage_dot<8>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = row_of_lane<8>(lane); break;
+                    case 4: tot = stage_dot<4>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = row_of_lane<4>(lane); break;
+                    case 2: tot = stage_dot<2>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = row_of_lane<2>(lane); break;
+                    default: tot = stage_dot<1>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = 0; break;
+                }
+            }
+            if ((lane & ((32 / g.nr) - 1)) == 0) sh.red[grp][i & 1][my_row][gwarp] = tot;
+            named_bar_sync(4 + grp, kDsGThreads);  // the whole group is done with slot s
+            if (sh.abort_flag) ok = false;
+            if (ok && gwarp == ((i + 4) & (kDsGWarps - 1)) && lane == 0)
+                issue_next_stage(p, emb, sh.cur[grp], grp, n_gemv, ring, sh.full_bar);
+
+            if (gwarp == (i & (kDsGWarps - 1)) && lane < g.nr) {
+                const float *rp = sh.red[grp][i & 1][lane];
+                float sum = ((rp[0] + rp[1]) + (rp[2] + rp[3])) + ((rp[4] + rp[5]) + (rp[6] + rp[7]));
+                const unsigned mask = (1u << g.nr) - 1u;
+                if (g.kind == PH_GU) {
+                    const float up = __shfl_down_sync(mask, sum, g.R);
+                    if (lane < rows) g.y[row0 + lane] = __float2half_rn(silu_ref(sum) * up);
+                } else if (g.kind == PH_LM) {
+                    const __half hv = __float2half_rn(sum);
+                    if (lane < rows) g.y[row0 + lane] = hv;
+                    float v = lane < rows ? __half2float(hv) : -INFINITY;
+                    if (!(v == v)) v = -INFINITY;  // NaN never wins
+                    int idx = row0 + lane;
+                    for (int m = g.nr >> 1; m >= 1; m >>= 1) {
+                        const float ov = __shfl_xor_sync(mask, v, m);
+                        const int oi = __shfl_xor_sync(mask, idx, m);
+                        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+                    }
+                    if (lane == 0 && (v > sh.best_val[grp] || (v == sh.best_val[grp] && idx < sh.best_idx[grp]))) {
+                        sh.best_val[grp] = v;
+                        sh.best_idx[grp] = idx;
+                    }
+                } else if (g.kind == PH_O || g.kind == PH_DOWN) {
+                    if (lane < rows) {
+                        const float o = __half2float(__float2half_rn(sum));
+                        // L2 load: other SMs wrote the residual stream earlier in this launch
+                        const __half out = __float2half_rn(o + __half2float(__ldcg(&g.res[row0 + lane])));
+                        g.y[row0 + lane] = out;
+                        if (g.hidden_row) g.hidden_row[row0 + lane] = out;
+                    }
+                } else {  // PH_QKV: RoPE on q and k rows, then q buffer / cache row `pos`
+                    const int row = row0 + lane;
+                    const float v = __half2float(__float2half_rn(sum));
+                    const float other = __shfl_xor_sync(mask, v, 1);
+                    if (lane < rows && pos >= 0 && pos < p.max_pos) {
+                        const DsLayer &L = p.layers[l];
+                        if (row < n_q + n_kv) {
+                            const int local = row < n_q ? row : row - n_q;
+                            const float2 cs = sh.rope_cs[(local >> 1) % (p.hd >> 1)];
+                            const float outv = (row & 1) ? __fmaf_rn(cs.y, other, __fmul_rn(cs.x, v))
+                                                         : __fmaf_rn(cs.x, v, -__fmul_rn(cs.y, other));
+                            const __half hv = __float2half_rn(outv);
+                            if (row < n_q) p.q[row] = hv;
+                            else L.k_cache[(size_t)pos * n_kv + local] = hv;
+                        } else {
+                            L.v_cache[(size_t)pos * n_kv + (row - n_q - n_kv)] = __float2half_rn(sum);
+                        }
+                    }
+                }
+            }
+        }
+        if (is_lm) {  // this CTA's best logit travels with the phase's arrival
+            named_bar_sync(3, kDsConsumers);
+            if (tid == 0) {
+                const bool second = sh.best_val[1] > sh.best_val[0] ||
+                                    (sh.best_val[1] == sh.best_val[0] && sh.best_idx[1] < sh.best_idx[0]);
+                p.amax_val[blockIdx.x] = sh.best_val[second ? 1 : 0];
+                p.amax_idx[blockIdx.x] = sh.best_idx[second ? 1 : 0];
+            }
+        }
+        grid_arrive();
+        stamp(tphase, 3);
+        ++tphase;
+
+        if (!is_lm && (ph & 3) == PH_QKV) {
+            // ------------------------------ attention ------------------------------
+            stamp(tphase, 0);
+            grid_wait();
+            stamp(tphase, 1);
+            const DsLayer &L = p.layers[l];
+            const int HD = p.hd;
+            const int chunks = HD >> 3;
+            const int len_total = pos + 1;
+            const int n_tasks = p.nkv * p.n_splits;
+            const float inv_den = sqrtf((float)HD);
+            int tpd = kDsConsumers / (kDsTile * G);  // threads per (row, head) dot product
+            tpd = tpd < 1 ? 1 : (tpd > 4 ? 4 : tpd);
+            const int n_out = G * HD;
+            for (int task = blockIdx.x; task < n_tasks && ok; task += gridDim.x) {
+                const int kvh = task / p.n_splits, split = task % p.n_splits;
+                const int begin = split * p.split_len;
+                const int end = min(begin + p.split_len, len_total);
+                named_bar_sync(1, kDsConsumers);
+                for (int i = tid; i < n_out; i += kDsConsumers) sh.q_s[i] = __half2float(__ldcg(&p.q[(size_t)kvh * n_out + i]));
+                if (tid < G) { sh.m_s[tid] = -INFINITY; sh.l_s[tid] = 0.0f; }
+                float acc[2] = {0.0f, 0.0f};
+                for (int t0 = begin; t0 < end; t0 += kDsTile) {
+                    const int rows = min(kDsTile, end - t0);
+                    named_bar_sync(1, kDsConsumers);  // previous tile consumed; q_s visible
+                    for (int c = tid; c < rows * chunks; c += kDsConsumers) {
+                        const int r = c / chunks, ch = c % chunks;
+                        const size_t goff = (size_t)(t0 + r) * n_kv + (size_t)kvh * HD + ch * 8;
+                        cp_async16_ds(&k_tile[r * HD + ((ch ^ (r & 7)) * 8)], L.k_cache + goff);
+                        cp_async16_ds(&v_tile[r * HD + ch * 8], L.v_cache + goff);
+                    }
+                    cp_async_wait_all_ds();
+                    named_bar_sync(1, kDsConsumers);
+                    // scores: dot = head * tile + row, split over tpd adjacent lanes
+                    {
+                        const int dot = tid / tpd, part = tid % tpd;
+                        const int hh = dot / kDsTile, r = dot % kDsTile;
+                        float sacc = 0.0f;
+                        if (hh < G && r < rows) {
+                            const int cpp = chunks / tpd;
+                            for (int cc = 0; cc < cpp; ++cc) {
+                                const int ch = part * cpp + cc;
+                                const uint4 kv = *reinterpret_cast<const uint4 *>(&k_tile[r * HD + ((ch ^ (r & 7)) * 8)]);
+                                const __half2 *kh = reinterpret_cast<const __half2 *>(&kv);
+                                const float *qp = &sh.q_s[hh * HD + ch * 8];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 f = __half22float2(kh[e]);
+                                    sacc = fmaf(qp[2 * e], f.x, sacc);
+                                    sacc = fmaf(qp[2 * e + 1], f.y, sacc);
+                                }
+                            }
+                        }
+                        for (int m = tpd >> 1; m >= 1; m >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, m);
+                        if (hh < G && part == 0) sh.p_s[hh * kDsTile + r] = (r < rows) ? __fdiv_rn(sacc, inv_den) : -INFINITY;
+                    }
+                    named_bar_sync(1, kDsConsumers);
+                    if (warp < G) {  // online softmax bookkeeping of head `warp` (one tile row per lane)
+                        static_assert(kDsTile == 32, "one score per lane");
+                        const float s0 = sh.p_s[warp * kDsTile + lane];
+                        const float tmax = warp_max(s0);
+                        const float m_old = sh.m_s[warp];
+                        const float m_new = fmaxf(m_old, tmax);
+                        const float sc = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
+                        const float e0 = (lane < rows) ? expf(s0 - m_new) : 0.0f;
+                        sh.p_s[warp * kDsTile + lane] = e0;
+                        const float ssum = warp_sum(e0);
+                        __syncwarp();
+                        if (lane == 0) {
+                            sh.scale_s[warp] = sc;
+                            sh.m_s[warp] = m_new;
+                            sh.l_s[warp] = sh.l_s[warp] * sc + ssum;
+                        }
+                    }
+                    named_bar_sync(1, kDsConsumers);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int o = tid + kDsConsumers * i;
+                        if (o < n_out) {
+                            const int hh = o / HD, dd = o % HD;
+                            float a = acc[i] * sh.scale_s[hh];
+                            const float *pp = &sh.p_s[hh * kDsTile];
+                            for (int r = 0; r < rows; ++r) a = fmaf(pp[r], __half2float(v_tile[r * HD + dd]), a);
+                            acc[i] = a;
+                        }
+                    }
+                }
+                named_bar_sync(1, kDsConsumers);
+                const size_t pbase = ((size_t)kvh * p.n_splits + split) * G;
+                if (tid < G) {
+                    p.part_ml[(pbase + tid) * 2] = sh.m_s[tid];
+                    p.part_ml[(pbase + tid) * 2 + 1] = sh.l_s[tid];
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int o = tid + kDsConsumers * i;
+                    if (o < n_out) p.part_o[(pbase + o / HD) * HD + (o % HD)] = acc[i];
+                }
+                __threadfence();
+                named_bar_sync(1, kDsConsumers);
+                if (tid == 0) {
+                    const int prev = atomicAdd(&p.attn_counters[kvh], 1);
+                    sh.is_last = (prev == p.n_splits - 1);
+                    if (sh.is_last) p.attn_counters[kvh] = 0;
+                }
+                named_bar_sync(1, kDsConsumers);
+                if (sh.is_last) {
+                    __threadfence();
+                    const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
+                    const size_t gbase = (size_t)kvh * p.n_splits * G;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int o = tid + kDsConsumers * i;
+                        if (o < n_out) {
+                            const int hh = o / HD, dd = o % HD;
+                            float M = -INFINITY;
+                            for (int sidx = 0; sidx < n_used; ++sidx)
+                                M = fmaxf(M, __ldcg(&p.part_ml[(gbase + (size_t)sidx * G + hh) * 2]));
+                            float num = 0.0f, den = 0.0f;
+                            for (int sidx = 0; sidx < n_used; ++sidx) {
+                                const size_t pi = gbase + (size_t)sidx * G + hh;
+                                const float m = __ldcg(&p.part_ml[pi * 2]);
+                                const float lsum = __ldcg(&p.part_ml[pi * 2 + 1]);
+                                const float wgt = (m == -INFINITY) ? 0.0f : expf(m - M);
+                                num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + dd]), num);
+                                den = fmaf(wgt, lsum, den);
+                            }
+                            p.attn[(size_t)kvh * n_out + o] = __float2half_rn(__fdiv_rn(num, den));
+                        }
+                    }
+                }
+            }
+            stamp(tphase, 2);
+            grid_arrive();
+            stamp(tphase, 3);
+            ++tphase;
+        }
+    }
+
+    // ---- step epilogue ----
+    grid_wait();  // every CTA has finished its last phase (and published its best logit)
+    if (blockIdx.x == 0 && warp == 0) {
+        int token = -1;
+        if (p.with_logits) {
+            float v = -INFINITY;
+            int idx = 0x7fffffff;
+            for (int c = lane; c < (int)gridDim.x; c += 32) {
+                const float ov = __ldcg(&p.amax_val[c]);
+                const int oi = __ldcg(&p.amax_idx[c]);
+                if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+            }
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, v, m);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, m);
+                if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+            }
+            token = idx == 0x7fffffff ? 0 : idx;
+        }
+        if (lane == 0) {
+            const int np = pos + 1;
+            if (p.with_logits) {
+                p.next_token[0] = token;
+                if (np < p.history_len) const_cast<int *>(p.history)[np] = token;
+            }
+            *p.pos = np;
+            p.bar[1] = bar_base + n_bar * (unsigned long long)gridDim.x;
+        }
+    }
+}
+
+}  // namespace llmb
+
+using namespace llmb;
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_splits <= 0) return 0;
+    return 256 + align256((size_t)n_kv_heads * 4) + align256((size_t)n_q_heads * max_splits * 2 * 4) +
+           align256((size_t)n_q_heads * max_splits * head_dim * 4) + align256(1024 * 4) + align256(1024 * 4);
+}
+
+extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t stream_) {
+    if (!a || !a->layers || !a->embed || !a->history || !a->pos || !a->x || !a->q || !a->attn || !a->h || !a->scratch)
+        return LLMB_ERR_INVALID;
+    if (a->with_logits && (!a->lm_head || !a->g_final || !a->logits || !a->next_token)) return LLMB_ERR_INVALID;
+    if (a->n_layers <= 0 || a->n_kv_heads <= 0 || a->n_q_heads % a->n_kv_heads || a->n_splits <= 0 ||
+        a->split_len <= 0 || (a->split_len % kDsTile) != 0 || a->n_splits > a->max_splits)
+        return LLMB_ERR_INVALID;
+    const int G = a->n_q_heads / a->n_kv_heads;
+    if ((a->head_dim != 64 && a->head_dim != 128) || G > 8 || G * a->head_dim > 2 * kDsConsumers) return LLMB_ERR_UNSUPPORTED;
+    if (a->d_model % 8 || a->ffn % 8 || a->d_model > 8192 || a->ffn > 16384 || a->n_q_heads * a->head_dim > 16384)
+        return LLMB_ERR_UNSUPPORTED;
+    if ((uintptr_t)a->scratch & 255) return LLMB_ERR_INVALID;
+    int dev = 0, sms = 0, coop = 0;
+    LLMB_CUDA_OK(cudaGetDevice(&dev));
+    LLMB_CUDA_OK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    if (!coop) return LLMB_ERR_UNSUPPORTED;
+    sms = sm_count_cached();
+    if (sms > 1024) sms = 1024;
+
+    DsParams p = {};
+    p.layers = reinterpret_cast<const DsLayer *>(a->layers);
+    p.embed = reinterpret_cast<const __half *>(a->embed);
+    p.lm_head = reinterpret_cast<const __half *>(a->lm_head);
+    p.g_final = reinterpret_cast<const __half *>(a->g_final);
+    p.history = a->history;
+    p.pos = a->pos;
+    p.x = reinterpret_cast<__half *>(a->x);
+    p.q = reinterpret_cast<__half *>(a->q);
+    p.attn = reinterpret_cast<__half *>(a->attn);
+    p.h = reinterpret_cast<__half *>(a->h);
+    p.logits = reinterpret_cast<__half *>(a->logits);
+    p.hidden = reinterpret_cast<__half *>(a->hidden);
+    p.next_token = a->next_token;
+    unsigned char *sc = static_cast<unsigned char *>(a->scratch);
+    p.bar = reinterpret_cast<unsigned long long *>(sc);
+    sc += 256;
+    p.attn_counters = reinterpret_cast<int *>(sc);
+    sc += align256((size_t)a->n_kv_heads * 4);
+    p.part_ml = reinterpret_cast<float *>(sc);
+    sc += align256((size_t)a->n_q_heads * a->max_splits * 2 * 4);
+    p.part_o = reinterpret_cast<float *>(sc);
+    sc += align256((size_t)a->n_q_heads * a->max_splits * a->head_dim * 4);
+    p.amax_val = reinterpret_cast<float *>(sc);
+    sc += align256(1024 * 4);
+    p.amax_idx = reinterpret_cast<int *>(sc);
+    p.status = device_status_ptr();
+    if (!p.status) return LLMB_ERR_CUDA;
+    p.trace = reinterpret_cast<unsigned long long *>(a->trace);
+    p.eps = a->eps;
+    p.rope_theta = a->rope_theta;
+    p.n_layers = a->n_layers;
+    p.d = a->d_model;
+    p.nq = a->n_q_heads;
+    p.nkv = a->n_kv_heads;
+    p.hd = a->head_dim;
+    p.ffn = a->ffn;
+    p.vocab = a->vocab;
+    p.embed_rows = a->embed_rows;
+    p.max_pos = a->max_pos;
+    p.n_splits = a->n_splits;
+    p.split_len = a->split_len;
+    p.with_logits = a->with_logits;
+    p.history_len = a->history_len;
+
+    const size_t smem = (size_t)kDsSlots * kDsSlotBytes + (size_t)2 * kDsTile * 128 * sizeof(__half);
+    static bool attr_set = false;
+    if (!attr_set) {
+        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms);
+    cfg.blockDim = dim3(kDsThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream_);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs co-resident or the launch fails
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LLMB_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_step_kernel, p));
+    return LLMB_OK;
+}

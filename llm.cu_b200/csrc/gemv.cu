@@ -21,7 +21,7 @@
 // The element-wise neighbours of each projection are fused in (see include/llm_b200.h).
 #include <cstdlib>
 
-#include "common.cuh"
+#include "gemv_common.cuh"
 
 namespace llmb {
 
@@ -47,60 +47,6 @@ struct GemvParams {
     int stages;
     uint32_t stage_bytes;  // smem bytes per stage
 };
-
-struct __align__(16) Half8 {
-    __half2 a, b, c, d;
-};
-
-__device__ __forceinline__ float dot8(const uint4 &wv, const float (&x)[8], float acc) {
-    const __half2 *h = reinterpret_cast<const __half2 *>(&wv);
-    float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]);
-    float2 f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-    acc = fmaf(f0.x, x[0], acc);
-    acc = fmaf(f0.y, x[1], acc);
-    acc = fmaf(f1.x, x[2], acc);
-    acc = fmaf(f1.y, x[3], acc);
-    acc = fmaf(f2.x, x[4], acc);
-    acc = fmaf(f2.y, x[5], acc);
-    acc = fmaf(f3.x, x[6], acc);
-    acc = fmaf(f3.y, x[7], acc);
-    return acc;
-}
-
-// Reduce NV per-lane values across the warp with NV-1 + (5 - log2 NV) shuffles.  Afterwards
-// lane l holds the warp total of value index row_of_lane<NV>(l).
-template <int NV>
-__device__ __forceinline__ float warp_reduce_multi(float (&v)[NV], int lane) {
-    int mask = 16;
-#pragma unroll
-    for (int step = NV / 2; step >= 1; step >>= 1) {
-        bool hi = (lane & mask) != 0;
-#pragma unroll
-        for (int i = 0; i < step; ++i) {
-            float send = hi ? v[i] : v[i + step];
-            float keep = hi ? v[i + step] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
-        }
-        mask >>= 1;
-    }
-    float r = v[0];
-    for (; mask >= 1; mask >>= 1) r += __shfl_xor_sync(0xffffffffu, r, mask);
-    return r;
-}
-
-template <int NV>
-__device__ __forceinline__ int row_of_lane(int lane) {
-    int row = 0, mask = 16;
-#pragma unroll
-    for (int step = NV / 2; step >= 1; step >>= 1) {
-        if (lane & mask) row += step;
-        mask >>= 1;
-    }
-    return row;
-}
-
-// SiLU exactly as the reference writes it (inference.cu:451-453).
-__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
 
 template <int J, int NR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
@@ -157,7 +103,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
 
     // ---------------- consumers ----------------
     const int nchunks = p.k >> 3;
-    float xr[J][8];
+    uint4 xh[J];  // this thread's chunks of the input row, packed FP16
     bool have[J];
 #pragma unroll
     for (int j = 0; j < J; ++j) have[j] = (tid + kConsumers * j) < nchunks;
@@ -171,22 +117,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
                             : make_uint4(0, 0, 0, 0);
     }
     pdl_wait();
-    {
-        uint4 xv[J];
 #pragma unroll
-        for (int j = 0; j < J; ++j)
-            xv[j] = have[j] ? *(reinterpret_cast<const uint4 *>(p.x) + tid + kConsumers * j) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const __half2 *h = reinterpret_cast<const __half2 *>(&xv[j]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float2 f = __half22float2(h[e]);
-                xr[j][2 * e] = f.x;
-                xr[j][2 * e + 1] = f.y;
-            }
-        }
-    }
+    for (int j = 0; j < J; ++j)
+        xh[j] = have[j] ? *(reinterpret_cast<const uint4 *>(p.x) + tid + kConsumers * j) : make_uint4(0, 0, 0, 0);
     if (p.prologue == LLMB_PRO_RMSNORM) {
         // Sum of squares in the order of the reference's block reduction
         // (inference.cu:309-344): one partial per four consecutive elements, then a binary
@@ -194,12 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
         // partials 2c and 2c+1, so tree levels with offset >= 512 pair values of one thread.
         float p0[J], p1[J];
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-            p0[j] = __fmaf_rn(xr[j][3], xr[j][3],
-                              __fmaf_rn(xr[j][2], xr[j][2], __fmaf_rn(xr[j][1], xr[j][1], xr[j][0] * xr[j][0])));
-            p1[j] = __fmaf_rn(xr[j][7], xr[j][7],
-                              __fmaf_rn(xr[j][6], xr[j][6], __fmaf_rn(xr[j][5], xr[j][5], xr[j][4] * xr[j][4])));
-        }
+        for (int j = 0; j < J; ++j) sumsq_partials(xh[j], p0[j], p1[j]);
 #pragma unroll
         for (int off = J / 2; off >= 1; off >>= 1) {
 #pragma unroll
@@ -231,40 +159,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
         named_bar_sync(1, kConsumers);
         const float rms = norm_rms;
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const __half2 *gh = reinterpret_cast<const __half2 *>(&gv[j]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float2 g = __half22float2(gh[e]);
-                // half((x * g) / rms), inference.cu:355-358
-                xr[j][2 * e] = __half2float(__float2half_rn(__fdiv_rn(xr[j][2 * e] * g.x, rms)));
-                xr[j][2 * e + 1] = __half2float(__float2half_rn(__fdiv_rn(xr[j][2 * e + 1] * g.y, rms)));
-            }
-        }
+        for (int j = 0; j < J; ++j)
+            if (have[j]) xh[j] = rmsnorm_apply8(xh[j], gv[j], rms);  // (0 * g) / rms would hit the division's slow path
     }
 
     bool ok = true;
     for (int g = g_begin, i = 0; g < g_end; ++g, ++i) {
         const int s = i % p.stages;
-        if (ok) ok = mbar_wait(&full_bar[s], (i / p.stages) & 1, p.status, 102);
+        if (ok) ok = mbar_wait_warp(&full_bar[s], (i / p.stages) & 1, p.status, 102, lane);
         const int row0 = g * R;
         const int rows = min(R, p.n - row0);
         float acc[NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
-        if (ok) {
-            const unsigned char *base = smem_raw + (size_t)s * p.stage_bytes;
-#pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                const int rr = DUAL ? (r % R) : r;
-                if (rr < rows) {
-                    const uint4 *rowp = reinterpret_cast<const uint4 *>(base + (size_t)r * row_bytes);
-#pragma unroll
-                    for (int j = 0; j < J; ++j)
-                        if (have[j]) acc[r] = dot8(rowp[tid + kConsumers * j], xr[j], acc[r]);
-                }
-            }
-        }
+        if (ok)
+            stage_dot_rows<NR, J, DUAL>(smem_raw + (size_t)s * p.stage_bytes, row_bytes, rows, tid, kConsumers, xh, have, acc);
         const float tot = warp_reduce_multi<NR>(acc, lane);
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(&empty_bar[s]);  // all lanes' smem reads are done

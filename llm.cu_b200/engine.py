@@ -70,8 +70,10 @@ class Cache:
         self._x = TensorStruct()
         self._d_tokens = None
 
-    def set_options(self, use_graph=-1, use_pdl=-1, copy_logits=-1):
+    def set_options(self, use_graph=-1, use_pdl=-1, copy_logits=-1, step_kernel=-1):
         check(lib.cache_set_options(self.ptr, int(use_graph), int(use_pdl), int(copy_logits)), "cache_set_options")
+        if step_kernel >= 0:
+            check(lib.cache_use_step_kernel(self.ptr, int(step_kernel)), "cache_use_step_kernel")
 
     def reset(self):
         check(lib.cache_reset(self.ptr), "cache_reset")

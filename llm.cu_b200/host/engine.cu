@@ -51,6 +51,13 @@ struct Engine {
     int *d_pos = nullptr, *d_next = nullptr, *d_history = nullptr;
     void *attn_scratch = nullptr;
     int max_splits = 0;
+    // whole-step persistent kernel
+    LlmbLayer *d_layers = nullptr;
+    void *step_scratch = nullptr;
+    size_t step_scratch_bytes = 0;
+    int step_max_splits = 0;
+    int sm_count = 148;
+    bool use_step_kernel = true;
     int *h_next = nullptr;  // pinned
     __half *hidden = nullptr;
     bool use_graph = true, use_pdl = true, copy_logits = true, hidden_dump = false;
@@ -178,12 +185,56 @@ int enqueue_step(Engine *e, bool with_logits, const SplitPlan &sp) {
     return LLMB_OK;
 }
 
-int kernels_per_step(const Engine *e, bool with_logits) { return 1 + 5 * e->layers + (with_logits ? 2 : 1); }
+int kernels_per_step(const Engine *e, bool with_logits) {
+    if (e->use_step_kernel) return 1;
+    return 1 + 5 * e->layers + (with_logits ? 2 : 1);
+}
+
+// The whole step as one persistent kernel.  Attention splits: 32-row tiles, doubled until the
+// task count fits about two waves of CTAs.
+int launch_step_kernel(Engine *e, bool with_logits, int len) {
+    const Llama3Config &c = e->model->config;
+    int split_len = 32;
+    while (e->nkv * ((len + split_len - 1) / split_len) > 2 * e->sm_count) split_len *= 2;
+    LlmbDecodeStepArgs a = {};
+    a.layers = e->d_layers;
+    a.n_layers = e->layers;
+    a.d_model = e->d;
+    a.n_q_heads = e->nq;
+    a.n_kv_heads = e->nkv;
+    a.head_dim = e->hd;
+    a.ffn = e->ffn;
+    a.vocab = e->vocab;
+    a.embed_rows = e->embed_rows;
+    a.max_pos = e->max_seq;
+    a.rope_theta = c.rope_theta;
+    a.eps = c.eps;
+    a.embed = reinterpret_cast<const uint16_t *>(e->model->embed_tokens->d_fp16_tensor);
+    a.lm_head = reinterpret_cast<const uint16_t *>(e->model->lm_head->d_fp16_tensor);
+    a.g_final = reinterpret_cast<const uint16_t *>(e->model->norm->d_fp16_tensor);
+    a.history = e->d_history;
+    a.history_len = e->max_seq;
+    a.pos = e->d_pos;
+    a.x = reinterpret_cast<uint16_t *>(e->x);
+    a.q = reinterpret_cast<uint16_t *>(e->q);
+    a.attn = reinterpret_cast<uint16_t *>(e->attn);
+    a.h = reinterpret_cast<uint16_t *>(e->h);
+    a.logits = reinterpret_cast<uint16_t *>(e->logits);
+    a.next_token = e->d_next;
+    a.scratch = e->step_scratch;
+    a.max_splits = e->step_max_splits;
+    a.split_len = split_len;
+    a.n_splits = (len + split_len - 1) / split_len;
+    a.with_logits = with_logits ? 1 : 0;
+    a.hidden = e->hidden_dump ? reinterpret_cast<uint16_t *>(e->hidden) : nullptr;
+    return llmb_decode_step(&a, e->stream);
+}
 
 // Runs one step for the token at history[pos]; `len` = pos + 1 is known on the host.
 int run_step(Engine *e, bool with_logits, int len) {
     const SplitPlan sp = plan_splits(len);
     e->launches += kernels_per_step(e, with_logits);
+    if (e->use_step_kernel) return launch_step_kernel(e, with_logits, len);
     if (!e->use_graph || e->hidden_dump) return enqueue_step(e, with_logits, sp);
     const int key = sp.bucket * 2 + (with_logits ? 1 : 0);
     auto it = e->graphs.find(key);
@@ -234,7 +285,7 @@ void destroy_engine(Engine *e) {
     for (auto &kv : e->graphs) cudaGraphExecDestroy(kv.second);
     cudaFree(e->x); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->h);
     cudaFree(e->rope_cs); cudaFree(e->d_pos); cudaFree(e->d_next); cudaFree(e->d_history);
-    cudaFree(e->attn_scratch); cudaFree(e->hidden);
+    cudaFree(e->attn_scratch); cudaFree(e->hidden); cudaFree(e->d_layers); cudaFree(e->step_scratch);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -302,6 +353,34 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
     alloc(reinterpret_cast<void **>(&e->d_next), 256);
     alloc(reinterpret_cast<void **>(&e->d_history), sizeof(int) * ((size_t)e->max_seq + 1));
     alloc(&e->attn_scratch, scratch);
+    e->sm_count = sm_count_cached();
+    e->step_max_splits = (e->max_seq + 31) / 32;
+    e->step_scratch_bytes = llmb_decode_step_scratch_bytes(e->nq, e->nkv, e->hd, e->step_max_splits);
+    alloc(&e->step_scratch, e->step_scratch_bytes);
+    alloc(reinterpret_cast<void **>(&e->d_layers), sizeof(LlmbLayer) * (size_t)e->layers);
+    if (ce == cudaSuccess) {
+        std::vector<LlmbLayer> hl((size_t)e->layers);
+        for (int l = 0; l < e->layers; ++l) {
+            const Llama3Layer *L = m->layers[l];
+            hl[l].wqkv = reinterpret_cast<const uint16_t *>(L->self_attn_q_proj->d_fp16_tensor);
+            hl[l].wo = reinterpret_cast<const uint16_t *>(L->self_attn_o_proj->d_fp16_tensor);
+            hl[l].wgate = reinterpret_cast<const uint16_t *>(L->mlp_gate_proj->d_fp16_tensor);
+            hl[l].wup = reinterpret_cast<const uint16_t *>(L->mlp_up_proj->d_fp16_tensor);
+            hl[l].wdown = reinterpret_cast<const uint16_t *>(L->mlp_down_proj->d_fp16_tensor);
+            hl[l].g_in = reinterpret_cast<const uint16_t *>(L->input_layernorm->d_fp16_tensor);
+            hl[l].g_post = reinterpret_cast<const uint16_t *>(L->post_attention_layernorm->d_fp16_tensor);
+            hl[l].k_cache = reinterpret_cast<uint16_t *>(e->kcache + (size_t)l * e->max_seq * n_kv);
+            hl[l].v_cache = reinterpret_cast<uint16_t *>(e->vcache + (size_t)l * e->max_seq * n_kv);
+        }
+        ce = cudaMemcpy(e->d_layers, hl.data(), sizeof(LlmbLayer) * hl.size(), cudaMemcpyHostToDevice);
+    }
+    {   // the persistent kernel needs a cooperative launch and shapes inside its limits
+        int dev = 0, coop = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        const int G = e->nq / e->nkv;
+        e->use_step_kernel = coop && G <= 8 && e->d <= 8192 && e->ffn <= 16384 && n_q <= 16384;
+    }
     if (ce == cudaSuccess) ce = cudaMallocHost(reinterpret_cast<void **>(&e->h_next), 256);
     for (auto &ev : e->ev)
         if (ce == cudaSuccess) ce = cudaEventCreate(&ev);
@@ -367,6 +446,16 @@ extern "C" int cache_reset(CudaCache *cache) {
     if (!e) return LLMB_ERR_INVALID;
     e->consumed.clear();
     e->greedy_state = false;
+    // also brings the step kernel's arrival counter back to a known state
+    LLMB_CUDA_OK(cudaMemsetAsync(e->step_scratch, 0, e->step_scratch_bytes, e->stream));
+    LLMB_CUDA_OK(cudaMemsetAsync(e->attn_scratch, 0, 256, e->stream));
+    return LLMB_OK;
+}
+
+extern "C" int cache_use_step_kernel(CudaCache *cache, int enable) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    e->use_step_kernel = enable != 0;
     return LLMB_OK;
 }
 

@@ -32,7 +32,7 @@ def ulp_diff(a_bits, b_bits):
     return np.abs(key(np.asarray(a_bits)) - key(np.asarray(b_bits)))
 
 
-def assert_close_fp16(got_bits, want_f64, max_ulp=1, max_frac=0.05, what=""):
+def assert_close_fp16(got_bits, want_f64, max_ulp=1, max_frac=0.05, what="", abs_tol=None):
     """got (FP16 bits) must equal RN(want) up to `max_ulp`, with at most `max_frac` of elements off at all:
     the kernels sum in FP32 in a different order than a sequential loop, which can move a value
     across an FP16 rounding boundary but never further.  Outputs that cancel to nearly zero have an
@@ -41,7 +41,10 @@ def assert_close_fp16(got_bits, want_f64, max_ulp=1, max_frac=0.05, what=""):
     want_f64 = np.asarray(want_f64, dtype=np.float64)
     want_bits = want_f64.astype(np.float16).view(np.uint16)
     d = ulp_diff(got_bits, want_bits)
-    abs_ok = np.abs(f16(got_bits).astype(np.float64) - want_f64) <= (1.0 + np.abs(want_f64).max()) * 2.0 ** -20
+    tol = (1.0 + np.abs(want_f64).max()) * 2.0 ** -20
+    if abs_tol is not None:
+        tol = np.maximum(tol, abs_tol)
+    abs_ok = np.abs(f16(got_bits).astype(np.float64) - want_f64) <= tol
     d = np.where(abs_ok & (d > max_ulp), max_ulp, d)
     assert d.max() <= max_ulp, "%s: max ulp distance %d" % (what, d.max())
     frac = float((d > 0).mean())

@@ -47,7 +47,8 @@ def test_oracle_matches_reference_binary(pkg, oracle):
 
 
 @pytest.mark.gpu
-def test_engine_matches_reference_binary(pkg, oracle):
+@pytest.mark.parametrize("step_kernel", [1, 0])
+def test_engine_matches_reference_binary(pkg, oracle, step_kernel):
     torch = pytest.importorskip("torch")
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
@@ -55,11 +56,12 @@ def test_engine_matches_reference_binary(pkg, oracle):
     cfg = pkg.CONFIGS[str(fx["config"])]
     model = pkg.Model.synthetic(cfg, seed=int(fx["seed"]), max_seq=256)
     cache = pkg.Cache(model)
+    cache.set_options(step_kernel=step_kernel)
     rows = []
     n_prompt = int(fx["n_prompt"])
     for s in range(len(fx["argmax"])):
         cache.infer(fx["tokens"][: n_prompt + s])
         rows.append(cache.logits())
-    compare(fx, rows, oracle, "engine")
+    compare(fx, rows, oracle, "engine (step kernel)" if step_kernel else "engine (per-op kernels)")
     cache.close()
     model.close()

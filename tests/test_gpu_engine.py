@@ -54,11 +54,12 @@ def teacher_forced(pkg, oracle, model, weights, tokens, n_prompt, check_hidden=F
     return dict(worst=worst, exact_rows=exact_rows, argmax_ok=argmax_ok, ties=ties, logits=all_logits)
 
 
-def test_tiny_teacher_forced_parity(pkg, oracle, tiny_weights):
+@pytest.mark.parametrize("step_kernel", [1, 0])
+def test_tiny_teacher_forced_parity(pkg, oracle, tiny_weights, step_kernel):
     cfg = pkg.CONFIGS["tiny"]
     tokens = oracle.synth_tokens(0, 16 + 32, cfg.vocab)
     model = pkg.Model.synthetic(cfg, seed=0, max_seq=128)
-    r = teacher_forced(pkg, oracle, model, tiny_weights, tokens, 16, check_hidden=True)
+    r = teacher_forced(pkg, oracle, model, tiny_weights, tokens, 16, check_hidden=True, step_kernel=step_kernel)
     assert r["ties"] <= 1 and r["argmax_ok"] >= 32
     print("tiny: worst |dlogit| %.4g, bit-exact rows %d/33" % (r["worst"], r["exact_rows"]))
     model.close()
@@ -68,7 +69,7 @@ def test_tiny_graph_pdl_and_plain_paths_agree_bitwise(pkg, oracle, tiny_weights)
     cfg = pkg.CONFIGS["tiny"]
     tokens = oracle.synth_tokens(0, 24, cfg.vocab)
     model = pkg.Model.synthetic(cfg, seed=0, max_seq=128)
-    runs = [teacher_forced(pkg, oracle, model, tiny_weights, tokens, 16, use_graph=g, use_pdl=p)["logits"]
+    runs = [teacher_forced(pkg, oracle, model, tiny_weights, tokens, 16, use_graph=g, use_pdl=p, step_kernel=0)["logits"]
             for g, p in ((1, 1), (0, 1), (0, 0), (1, 0))]
     for other in runs[1:]:
         for a, b in zip(runs[0], other):
@@ -96,15 +97,17 @@ def test_tiny_safetensors_load_path_matches_synthetic(pkg, oracle, tiny_weights,
     assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1])
 
 
-def test_greedy_device_loop_equals_step_by_step(pkg, oracle):
+@pytest.mark.parametrize("step_kernel", [1, 0])
+def test_greedy_device_loop_equals_step_by_step(pkg, oracle, step_kernel):
     cfg = pkg.CONFIGS["tiny"]
     prompt = oracle.synth_tokens(0, 16, cfg.vocab).tolist()
     model = pkg.Model.synthetic(cfg, seed=0, max_seq=128)
     cache = pkg.Cache(model)
+    cache.set_options(step_kernel=step_kernel)
     toks, pre_ms, dec_ms = cache.greedy(prompt, 32)
     assert pre_ms > 0 and dec_ms > 0
     launches = cache.kernel_launches()
-    assert launches == 15 * (1 + 5 * 2 + 1) + 32 * (1 + 5 * 2 + 2)
+    assert launches == (15 + 32 if step_kernel else 15 * (1 + 5 * 2 + 1) + 32 * (1 + 5 * 2 + 2))
     cache.reset()
     seq = list(prompt)
     for _ in range(32):
@@ -131,14 +134,39 @@ def test_bf16_load_conversion_model(pkg, oracle):
     model.close()
 
 
-def test_8b_layer_shapes_two_layers(pkg, oracle):
+@pytest.fixture(scope="module")
+def weights_8b_l2(pkg, oracle):
+    return oracle.Weights(pkg.CONFIGS["llama3_8b_l2"], seed=0, keep_file=False)
+
+
+@pytest.mark.parametrize("step_kernel", [1, 0])
+def test_8b_layer_shapes_two_layers(pkg, oracle, weights_8b_l2, step_kernel):
     """LLaMA3-8B layer shape (d 4096, 32/8 heads, ffn 14336, vocab 128256), two layers."""
     cfg = pkg.CONFIGS["llama3_8b_l2"]
-    w = oracle.Weights(cfg, seed=0)
+    w = weights_8b_l2
     tokens = oracle.synth_tokens(0, 16 + 8, cfg.embed_rows)
     model = pkg.Model.synthetic(cfg, seed=0, max_seq=256)
-    r = teacher_forced(pkg, oracle, model, w, tokens, 16, check_hidden=True)
+    r = teacher_forced(pkg, oracle, model, w, tokens, 16, check_hidden=True, step_kernel=step_kernel)
     print("8b_l2: worst |dlogit| %.4g, bit-exact rows %d/9, ties %d" % (r["worst"], r["exact_rows"], r["ties"]))
+    model.close()
+
+
+def test_step_kernel_long_context_matches_per_op_kernels(pkg, oracle):
+    """Several attention tiles and splits: 700 cached rows, both decode paths, same tokens and logits
+    within the FP16 tolerance (the two paths split the sums differently)."""
+    cfg = pkg.CONFIGS["tiny"]
+    prompt = oracle.synth_tokens(5, 700, cfg.vocab).tolist()
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=1024)
+    outs = []
+    for sk in (1, 0):
+        cache = pkg.Cache(model)
+        cache.set_options(step_kernel=sk)
+        toks, _, _ = cache.greedy(prompt, 6)
+        cache.infer(prompt + toks)
+        outs.append((toks, oracle.f16(cache.logits())))
+        cache.close()
+    assert outs[0][0] == outs[1][0]
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 4e-3
     model.close()
 
 
