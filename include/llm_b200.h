@@ -192,8 +192,8 @@ typedef struct {
     int n_splits, split_len;
     int with_logits;
     uint16_t *hidden;       /* optional [n_layers + 1][d_model]: residual stream after each layer */
-    uint64_t *trace;        /* optional profiling aid, device [4][5 * n_layers + 2][4] nanosecond stamps:
-                               CTAs 0, 1, middle, last; per phase: entered, dependency met, input ready,
+    uint64_t *trace;        /* optional profiling aid, device [SM count][5 * n_layers + 2][4] nanosecond
+                               stamps, one row per CTA; per phase: entered, dependency met, input ready,
                                done.  NULL in production. */
 } LlmbDecodeStepArgs;
 

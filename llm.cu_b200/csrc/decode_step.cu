@@ -3,10 +3,10 @@
 // row, without a kernel boundary between its phases.
 //
 // Why: at batch 1 a layer is five dependent phases of 5-36 us each.  As separate kernels each
-// boundary drains and refills the memory pipeline; here a producer thread streams the weights of
-// every projection, in program order, through one shared-memory ring with 1-D bulk copies and
-// runs ahead of the math across phase boundaries, so HBM keeps working while the CTAs
-// synchronise.  The phases are the fused operations of gemv.cu / attn_decode.cu:
+// boundary drains and refills the memory pipeline; here the weights of every projection stream, in
+// program order, through one shared-memory ring of 1-D bulk copies that runs ahead of the math
+// across phase boundaries, so HBM keeps working while the CTAs synchronise.  The phases are the
+// fused operations of gemv.cu / attn_decode.cu:
 //
 //   per layer   QKV    RMSNorm(x) -> [q;k;v] rows -> RoPE -> q buffer / KV-cache row `pos`
 //               ATTN   split-KV softmax(q K^T / sqrt(hd)) V, last CTA per KV head merges
@@ -19,26 +19,35 @@
 // Bound: HBM.  Algorithmic bytes per launch = all projection weights + lm_head + norm gains + one
 // embedding row + (pos + 1) KV rows read + one KV row written.
 //
-// Synchronisation: a monotonically increasing 64-bit arrival counter in global memory; phase p of
-// a launch waits for base + (p + 1) * gridDim.x, and CTA 0 stores the next launch's base at the
-// end.  Every wait (mbarrier or counter) is bounded: on expiry the CTA records a status code,
-// stops waiting for anything else and runs to the end without touching the ring.
+// Roles inside a CTA (17 warps)
+//   warps 0-15  two consumer groups of 8 warps; ring stage `it` belongs to group it % 2.  A thread
+//               holds its 16-byte chunks of the input row in registers, multiplies them with the
+//               stage's rows (mixed-precision FMA, FP32 accumulate), the warp reduces and leaves one
+//               partial per row in shared memory, then moves on: consumer warps never wait for each
+//               other, only for data.
+//   warp 16     the stage finisher: waits until the 8 partials of a stage are there, adds them in
+//               warp order, applies the epilogue (RoPE + cache append / residual add / SwiGLU /
+//               logit + argmax) and refills the ring slot with the stage six ahead.
+// Grid-wide order between phases: a monotonically increasing 64-bit arrival counter in global
+// memory; the k-th wait of a launch needs base + k * gridDim.x arrivals, and CTA 0 stores the next
+// launch's base at the end.  Every wait (mbarrier or counter) is bounded: on expiry the CTA records
+// a status code, stops waiting for anything else and runs to the end.
 #include <cstdlib>
 
 #include "gemv_common.cuh"
 
 namespace llmb {
 
-constexpr int kDsWarps = 16;                  // consumer warps
-constexpr int kDsConsumers = kDsWarps * 32;   // 512
-constexpr int kDsThreads = kDsConsumers;      // no dedicated producer: 4 warps per scheduler at 128 registers
-constexpr int kDsGroups = 2;                  // consumer groups; group g owns ring stages with it % 2 == g
+constexpr int kDsWarps = 16;                      // consumer warps
+constexpr int kDsConsumers = kDsWarps * 32;       // 512
+constexpr int kDsThreads = kDsConsumers + 32;     // + the stage finisher
+constexpr int kDsGroups = 2;
 constexpr int kDsGWarps = kDsWarps / kDsGroups;   // 8
 constexpr int kDsGThreads = kDsGWarps * 32;       // 256
 constexpr int kDsSlots = 6;
 constexpr uint32_t kDsSlotBytes = 32 * 1024;
-constexpr int kDsJ = 8;                       // 16-byte chunks of x per thread: k <= 16384
-constexpr int kDsTile = 32;                   // cache rows per attention tile
+constexpr int kDsJ = 8;                           // 16-byte chunks of x per thread: k <= 16384
+constexpr int kDsTile = 32;                       // cache rows per attention tile
 constexpr uint32_t kPollLimit = 1u << 22;
 
 struct DsLayer {
@@ -59,7 +68,7 @@ struct DsParams {
     float *amax_val;          // [gridDim]
     int *amax_idx;
     int *status;
-    unsigned long long *trace;  // optional: [4 CTAs][phases][4] globaltimer stamps
+    unsigned long long *trace;  // optional: [gridDim][phases][4] globaltimer stamps
     double eps;
     float rope_theta;
     int n_layers, d, nq, nkv, hd, ffn, vocab, embed_rows, max_pos;
@@ -70,7 +79,7 @@ enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
 
 struct GemvDesc {
     const __half *w, *w2, *x, *gamma, *res;
-    __half *y, *hidden_row;
+    __half *y, *hidden_row, *k_cache, *v_cache;
     int n, k, nr, R, kind;
 };
 
@@ -79,21 +88,26 @@ __device__ __forceinline__ int rows_per_stage(int k) {
     return fit >= 8 ? 8 : (fit >= 4 ? 4 : (fit >= 2 ? 2 : 1));
 }
 
-// Projection `kind` of layer `l` (l ignored for PH_LM).  `emb` is the embedding row of this step.
-__device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, int l, int kind, const __half *emb) {
+// Projection number `ph` of the step: 4 * layer + {QKV, O, GU, DOWN}, then the lm_head.
+// `emb` is the embedding row of this step's token.
+__device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, const DsLayer *layers, int ph, const __half *emb) {
     GemvDesc g;
+    const int l = ph >> 2;
+    const int kind = (ph < 4 * p.n_layers) ? (ph & 3) : PH_LM;
     g.kind = kind;
     g.w2 = nullptr;
     g.gamma = nullptr;
     g.res = nullptr;
     g.hidden_row = nullptr;
+    g.k_cache = g.v_cache = nullptr;
     const int nq = p.nq * p.hd, nkv = p.nkv * p.hd;
     if (kind == PH_LM) {
         g.w = p.lm_head; g.x = p.x; g.gamma = p.g_final; g.y = p.logits; g.n = p.vocab; g.k = p.d;
     } else {
-        const DsLayer &L = p.layers[l];
+        const DsLayer &L = layers[l];
         if (kind == PH_QKV) {
             g.w = L.wqkv; g.x = (l == 0) ? emb : p.x; g.gamma = L.g_in; g.y = p.q; g.n = nq + 2 * nkv; g.k = p.d;
+            g.k_cache = L.k_cache; g.v_cache = L.v_cache;
         } else if (kind == PH_O) {
             g.w = L.wo; g.x = p.attn; g.res = (l == 0) ? emb : p.x; g.y = p.x; g.n = p.d; g.k = nq;
         } else if (kind == PH_GU) {
@@ -130,18 +144,11 @@ __device__ __forceinline__ void cp_async16_ds(void *smem_dst, const void *gsrc) 
 }
 __device__ __forceinline__ void cp_async_wait_all_ds() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// Where a consumer group's weight stream stands: the next ring stage to request.
-struct DsCursor {
-    const unsigned char *w, *w2;
-    size_t row_bytes;
-    int ph, rg, rg_end, n, R;
-    uint32_t it;
-};
-
 struct DsShared {
-    uint64_t full_bar[kDsSlots];
-    DsCursor cur[kDsGroups];
-    float red[kDsGroups][2][8][kDsGWarps];
+    uint64_t full_bar[kDsSlots];   // stage data has landed (bulk-copy byte count)
+    uint64_t done_bar[kDsSlots];   // the 8 consumer warps of the stage have left their partials
+    float red[kDsSlots][8][kDsGWarps];
+    float res_s[128];  // this CTA's slice of the residual stream for the current projection
     float norm_buf[kDsGroups][512];
     float2 rope_cs[64];
     float q_s[8 * 128];
@@ -149,45 +156,42 @@ struct DsShared {
     float scale_s[8];
     float m_s[8], l_s[8];
     float norm_rms[kDsGroups];
-    float best_val[kDsGroups];
-    int best_idx[kDsGroups];
     int abort_flag;
     int is_last;
 };
 
-// Requests the next ring stage that belongs to consumer group `grp` (stages alternate between the
-// groups), walking on through the projections in program order.  Called by one thread of the group
-// right after the group has finished with the slot that stage maps to.
-__device__ __noinline__ void issue_next_stage(const DsParams &p, const __half *emb, DsCursor &c, int grp, int n_gemv,
-                                              unsigned char *ring, uint64_t *full_bar) {
-    for (;;) {
-        if (c.ph >= n_gemv) return;
-        if (c.rg >= c.rg_end) {
-            if (++c.ph >= n_gemv) return;
-            const GemvDesc g = gemv_desc(p, c.ph >> 2, (c.ph < 4 * p.n_layers) ? (c.ph & 3) : PH_LM, emb);
-            c.w = reinterpret_cast<const unsigned char *>(g.w);
-            c.w2 = reinterpret_cast<const unsigned char *>(g.w2);
-            c.row_bytes = (size_t)g.k * 2;
-            c.n = g.n;
-            c.R = g.R;
-            cta_range((g.n + g.R - 1) / g.R, c.rg, c.rg_end);
-            continue;
-        }
-        const uint32_t it = c.it++;
-        const int rg = c.rg++;
-        if ((int)(it % kDsGroups) != grp) continue;
-        const int s = it % kDsSlots;
-        const int row0 = rg * c.R;
-        const int rows = min(c.R, c.n - row0);
-        unsigned char *dst = ring + (size_t)s * kDsSlotBytes;
-        const uint32_t bytes = (uint32_t)(rows * c.row_bytes);
-        const uint64_t policy = policy_evict_first();
-        fence_proxy_async();  // the slot was last read through the generic proxy
-        mbar_arrive_expect_tx(&full_bar[s], c.w2 ? 2 * bytes : bytes);
-        bulk_g2s(dst, c.w + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
-        if (c.w2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, c.w2 + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
-        return;
+// Where the finisher's weight stream stands: the next ring stage to request.
+struct DsCursor {
+    const unsigned char *w, *w2;
+    size_t row_bytes;
+    int ph, rg, rg_end, n, R;
+    uint32_t it;
+};
+
+// Requests the next ring stage, walking on through the projections in program order.
+__device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv,
+                                                 unsigned char *ring, uint64_t *full_bar, uint64_t policy) {
+    while (c.rg >= c.rg_end) {
+        if (c.ph + 1 >= n_gemv) { c.ph = n_gemv; return; }
+        ++c.ph;
+        const GemvDesc g = gemv_desc(p, layers, c.ph, emb);
+        c.w = reinterpret_cast<const unsigned char *>(g.w);
+        c.w2 = reinterpret_cast<const unsigned char *>(g.w2);
+        c.row_bytes = (size_t)g.k * 2;
+        c.n = g.n;
+        c.R = g.R;
+        cta_range((g.n + g.R - 1) / g.R, c.rg, c.rg_end);
     }
+    const int s = c.it % kDsSlots;
+    const int row0 = c.rg * c.R;
+    const int rows = min(c.R, c.n - row0);
+    unsigned char *dst = ring + (size_t)s * kDsSlotBytes;
+    const uint32_t bytes = (uint32_t)(rows * c.row_bytes);
+    mbar_arrive_expect_tx(&full_bar[s], c.w2 ? 2 * bytes : bytes);
+    bulk_g2s(dst, c.w + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
+    if (c.w2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, c.w2 + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
+    ++c.it;
+    ++c.rg;
 }
 
 template <int NR>
@@ -214,20 +218,21 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     unsigned char *ring = ds_smem;
     __half *k_tile = reinterpret_cast<__half *>(ds_smem + (size_t)kDsSlots * kDsSlotBytes);
     __half *v_tile = k_tile + kDsTile * 128;
+    // the per-layer pointer table, copied once: phase switches must not wait on global memory
+    DsLayer *layer_s = reinterpret_cast<DsLayer *>(v_tile + kDsTile * 128);
     __shared__ DsShared sh;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kDsSlots; ++s) {
             mbar_init(&sh.full_bar[s], 1);
+            mbar_init(&sh.done_bar[s], kDsGWarps);
         }
         fence_mbar_init();
         sh.abort_flag = 0;
-        for (int g = 0; g < kDsGroups; ++g) {
-            sh.best_val[g] = -INFINITY;
-            sh.best_idx[g] = 0x7fffffff;
-        }
     }
+    for (int i = threadIdx.x; i < p.n_layers * (int)(sizeof(DsLayer) / 8); i += kDsThreads)
+        reinterpret_cast<unsigned long long *>(layer_s)[i] = reinterpret_cast<const unsigned long long *>(p.layers)[i];
     __syncthreads();
 
     const int pos = *p.pos;
@@ -235,35 +240,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     tok = tok < 0 ? 0 : (tok >= p.embed_rows ? p.embed_rows - 1 : tok);
     const __half *emb = p.embed + (size_t)tok * p.d;
     const int n_gemv = 4 * p.n_layers + (p.with_logits ? 1 : 0);
-
-    const int grp = warp / kDsGWarps;   // consumer group of this warp
-    const int gwarp = warp % kDsGWarps;  // warp index inside the group
-    const int gtid = tid % kDsGThreads;  // thread index inside the group
-    // Start the weight stream: each group requests its first kDsSlots / 2 stages.
-    if (gtid == 0) {
-        DsCursor &c = sh.cur[grp];
-        c.ph = -1;
-        c.rg = c.rg_end = 0;
-        c.it = 0;
-        for (int k = 0; k < kDsSlots / kDsGroups; ++k) issue_next_stage(p, emb, c, grp, n_gemv, ring, sh.full_bar);
-    }
-    // RoPE angles of this position (inference.cu:673-678), once per CTA.
-    if (tid < p.hd / 2) {
-        const float freq = 1.0f / powf(p.rope_theta, 2.0f * (float)tid / (float)p.hd);
-        const float angle = (float)pos * freq;
-        sh.rope_cs[tid] = make_float2(cosf(angle), sinf(angle));
-    }
-    if (p.hidden && blockIdx.x == 0)
-        for (int i = tid; i < p.d; i += kDsConsumers) p.hidden[i] = emb[i];
-
+    const int n_q = p.nq * p.hd, n_kv = p.nkv * p.hd;
     const unsigned long long bar_base = p.bar[1];
-    unsigned long long n_bar = 0;  // barriers passed in this launch
-    bool ok = true;
-    uint32_t it = 0;
+    unsigned long long n_bar = 0;  // grid-wide waits passed in this launch
+    bool ok = true;                // only changes right after a barrier of all 17 warps
 
-    // arrive: every global write of this CTA for the finished phase is ordered before the count
+    // End of a phase for this CTA: all its global writes are ordered before the arrival.
     auto grid_arrive = [&]() {
-        named_bar_sync(3, kDsConsumers);
+        named_bar_sync(3, kDsThreads);
         if (tid == 0) {
             __threadfence();
             atomicAdd(p.bar, 1ULL);
@@ -282,40 +266,146 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 }
             }
         }
-        named_bar_sync(3, kDsConsumers);
+        named_bar_sync(3, kDsThreads);
         if (sh.abort_flag) ok = false;
     };
 
-    const int n_q = p.nq * p.hd, n_kv = p.nkv * p.hd;
-    const int G = p.nq / p.nkv;
-    // profiling aid: CTAs 0, 1, mid and last stamp the global timer four times per phase
-    int trace_row = -1;
-    if (p.trace && tid == 0) {
-        const int b = blockIdx.x, gdim = gridDim.x;
-        trace_row = b == 0 ? 0 : (b == 1 ? 1 : (b == gdim / 2 ? 2 : (b == gdim - 1 ? 3 : -1)));
+    if (warp == kDsWarps) {
+        // =========================== stage finisher ===========================
+        const uint64_t policy = policy_evict_first();
+        DsCursor cur;
+        cur.ph = -1;
+        cur.rg = cur.rg_end = 0;
+        cur.it = 0;
+        cur.w = cur.w2 = nullptr;
+        cur.row_bytes = 0;
+        cur.n = cur.R = 0;
+        if (lane == 0)
+            for (int k = 0; k < kDsSlots; ++k) issue_next_stage(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+        float best_val = -INFINITY;
+        int best_idx = 0x7fffffff;
+        uint32_t it = 0;
+        for (int ph = 0; ph < n_gemv; ++ph) {
+            const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
+            if (ph > 0) grid_wait();
+            int gb, ge;
+            cta_range((g.n + g.R - 1) / g.R, gb, ge);
+            const unsigned mask = (1u << g.nr) - 1u;
+            // Residual rows of this CTA: one batch of L2 loads per phase, not one round trip per stage.
+            const int res_rows = g.res ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
+            const bool res_cached = res_rows <= 128;
+            if (res_cached) {
+                for (int i = lane; i < res_rows; i += 32) sh.res_s[i] = __half2float(__ldcg(&g.res[gb * g.R + i]));
+                __syncwarp();
+            }
+            for (int rg = gb; rg < ge; ++rg, ++it) {
+                const int s = it % kDsSlots;
+                const int row0 = rg * g.R;
+                const int rows = min(g.R, g.n - row0);
+                float res = 0.0f;
+                if (g.res && lane < rows)
+                    res = res_cached ? sh.res_s[row0 - gb * g.R + lane] : __half2float(__ldcg(&g.res[row0 + lane]));
+                bool got = false;
+                if (ok) {
+                    got = mbar_wait_warp(&sh.done_bar[s], (it / kDsSlots) & 1, p.status, 204, lane);
+                    if (!got) sh.abort_flag = 1;
+                }
+                if (got && lane < g.nr) {
+                    const float *rp = sh.red[s][lane];
+                    const float sum = ((rp[0] + rp[1]) + (rp[2] + rp[3])) + ((rp[4] + rp[5]) + (rp[6] + rp[7]));
+                    if (g.kind == PH_GU) {
+                        const float up = __shfl_down_sync(mask, sum, g.R);
+                        if (lane < rows) g.y[row0 + lane] = __float2half_rn(silu_ref(sum) * up);
+                    } else if (g.kind == PH_LM) {
+                        const __half hv = __float2half_rn(sum);
+                        if (lane < rows) g.y[row0 + lane] = hv;
+                        float v = lane < rows ? __half2float(hv) : -INFINITY;
+                        if (!(v == v)) v = -INFINITY;  // NaN never wins
+                        int idx = row0 + lane;
+                        for (int m = g.nr >> 1; m >= 1; m >>= 1) {
+                            const float ov = __shfl_xor_sync(mask, v, m);
+                            const int oi = __shfl_xor_sync(mask, idx, m);
+                            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+                        }
+                        if (v > best_val || (v == best_val && idx < best_idx)) { best_val = v; best_idx = idx; }
+                    } else if (g.kind == PH_O || g.kind == PH_DOWN) {
+                        if (lane < rows) {
+                            const float o = __half2float(__float2half_rn(sum));
+                            const __half out = __float2half_rn(o + res);
+                            g.y[row0 + lane] = out;
+                            if (g.hidden_row) g.hidden_row[row0 + lane] = out;
+                        }
+                    } else {  // PH_QKV: RoPE on q and k rows, then q buffer / cache row `pos`
+                        const int row = row0 + lane;
+                        const float v = __half2float(__float2half_rn(sum));
+                        const float other = __shfl_xor_sync(mask, v, 1);
+                        if (lane < rows && pos >= 0 && pos < p.max_pos) {
+                            if (row < n_q + n_kv) {
+                                const int local = row < n_q ? row : row - n_q;
+                                const float2 cs = sh.rope_cs[(local >> 1) % (p.hd >> 1)];
+                                const float outv = (row & 1) ? __fmaf_rn(cs.y, other, __fmul_rn(cs.x, v))
+                                                             : __fmaf_rn(cs.x, v, -__fmul_rn(cs.y, other));
+                                const __half hv = __float2half_rn(outv);
+                                if (row < n_q) p.q[row] = hv;
+                                else g.k_cache[(size_t)pos * n_kv + local] = hv;
+                            } else {
+                                g.v_cache[(size_t)pos * n_kv + (row - n_q - n_kv)] = __float2half_rn(sum);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                // slot s is free (all 8 warps have read it) and its partials are consumed: refill
+                if (lane == 0 && got) issue_next_stage(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+            }
+            if (g.kind == PH_LM && lane == 0) {  // this CTA's best logit travels with the phase's arrival
+                p.amax_val[blockIdx.x] = best_val;
+                p.amax_idx[blockIdx.x] = best_idx;
+            }
+            grid_arrive();
+            if (g.kind == PH_QKV) {  // the consumers' attention phase: keep in step with its barriers
+                grid_wait();
+                grid_arrive();
+            }
+        }
+        grid_wait();
+        return;
     }
+
+    // =============================== consumers ===============================
+    const int grp = warp / kDsGWarps;   // consumer group of this warp
+    const int gwarp = warp % kDsGWarps;  // warp index inside the group
+    const int gtid = tid % kDsGThreads;  // thread index inside the group
+    // RoPE angles of this position (inference.cu:673-678), once per CTA.
+    if (tid < p.hd / 2) {
+        const float freq = 1.0f / powf(p.rope_theta, 2.0f * (float)tid / (float)p.hd);
+        const float angle = (float)pos * freq;
+        sh.rope_cs[tid] = make_float2(cosf(angle), sinf(angle));
+    }
+    if (p.hidden && blockIdx.x == 0)
+        for (int i = tid; i < p.d; i += kDsConsumers) p.hidden[i] = emb[i];
+
+    const int G = p.nq / p.nkv;
+    // profiling aid: thread 0 of every CTA stamps the global timer four times per phase
+    const int trace_row = (p.trace && tid == 0) ? (int)blockIdx.x : -1;
     auto stamp = [&](int phase, int which) {
         if (trace_row >= 0) p.trace[((size_t)trace_row * (5 * p.n_layers + 2) + phase) * 4 + which] = globaltimer_ns();
     };
     int tphase = 0;
+    uint32_t it = 0;
 
-    int gi = 0;                          // stages this group has processed (red double buffer)
-
-    for (int ph = 0; ph <= 4 * p.n_layers; ++ph) {
-        const bool is_lm = ph == 4 * p.n_layers;
-        if (is_lm && !p.with_logits) break;
-        const int l = ph >> 2;
-        const GemvDesc g = gemv_desc(p, l, is_lm ? PH_LM : (ph & 3), emb);
+    for (int ph = 0; ph < n_gemv; ++ph) {
+        const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
         const int nchunks = g.k >> 3;
         const size_t row_bytes = (size_t)g.k * 2;
         bool have[kDsJ];
 #pragma unroll
         for (int j = 0; j < kDsJ; ++j) have[j] = (gtid + kDsGThreads * j) < nchunks;
         stamp(tphase, 0);
-        if (g.gamma) {  // the gain vector does not depend on the previous phase: bring it to L2 now
+        if (g.gamma && grp == 0) {  // the gain vector does not depend on the previous phase: bring it to L2 now
 #pragma unroll
-            for (int j = 0; j < kDsJ; ++j)
-                if (have[j] && grp == 0)
+            for (int j = 0; j < kDsJ / 2; ++j)
+                if (have[j])
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4 *>(g.gamma) + gtid + kDsGThreads * j));
         }
         if (ph > 0) grid_wait();  // the phase that produced x has finished everywhere
@@ -334,8 +424,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             for (int j = 0; j < kNormJ; ++j)
                 gv[j] = have[j] ? __ldg(reinterpret_cast<const uint4 *>(g.gamma) + gtid + kDsGThreads * j)
                                 : make_uint4(0, 0, 0, 0);
-        }
-        if (g.gamma) {
             // Sum of squares in the reference's reduction order (inference.cu:309-344): a partial per
             // four consecutive elements, then a binary tree with offsets halving from (k/4)/2.  Chunk
             // c = t + 256 j holds partials 2c, 2c+1: offsets >= 512 stay inside a thread, 256..64 cross
@@ -377,23 +465,19 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         }
         stamp(tphase, 2);
 
-        // ---- stream this CTA's row groups: ring stage `it` belongs to consumer group it % 2 ----
+        // ---- this CTA's row groups: ring stage `it` belongs to consumer group it % 2 ----
         int gb, ge;
         cta_range((g.n + g.R - 1) / g.R, gb, ge);
         const bool dual = g.w2 != nullptr;
         for (int rg = gb; rg < ge; ++rg, ++it) {
             if ((int)(it % kDsGroups) != grp) continue;
             const int s = it % kDsSlots;
-            const int i = gi++;
-            // `ok` only changes right after a barrier of the whole group, so that every thread of the
-            // group takes the same path through the barriers below even when a wait gives up.
             bool got = false;
             if (ok) {
                 got = mbar_wait_warp(&sh.full_bar[s], (it / kDsSlots) & 1, p.status, 203, lane);
                 if (!got) sh.abort_flag = 1;
             }
-            const int row0 = rg * g.R;
-            const int rows = min(g.R, g.n - row0);
+            const int rows = min(g.R, g.n - rg * g.R);
             const unsigned char *base = ring + (size_t)s * kDsSlotBytes;
             float tot = 0.0f;
             int my_row = 0;
@@ -404,83 +488,20 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     case 2: tot = stage_dot<2>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = row_of_lane<2>(lane); break;
                     default: tot = stage_dot<1>(base, row_bytes, rows, dual, xh, have, gtid, lane); my_row = 0; break;
                 }
-            }
-            if ((lane & ((32 / g.nr) - 1)) == 0) sh.red[grp][i & 1][my_row][gwarp] = tot;
-            named_bar_sync(4 + grp, kDsGThreads);  // the whole group is done with slot s
-            if (sh.abort_flag) ok = false;
-            if (ok && gwarp == ((i + 4) & (kDsGWarps - 1)) && lane == 0)
-                issue_next_stage(p, emb, sh.cur[grp], grp, n_gemv, ring, sh.full_bar);
-
-            if (gwarp == (i & (kDsGWarps - 1)) && lane < g.nr) {
-                const float *rp = sh.red[grp][i & 1][lane];
-                float sum = ((rp[0] + rp[1]) + (rp[2] + rp[3])) + ((rp[4] + rp[5]) + (rp[6] + rp[7]));
-                const unsigned mask = (1u << g.nr) - 1u;
-                if (g.kind == PH_GU) {
-                    const float up = __shfl_down_sync(mask, sum, g.R);
-                    if (lane < rows) g.y[row0 + lane] = __float2half_rn(silu_ref(sum) * up);
-                } else if (g.kind == PH_LM) {
-                    const __half hv = __float2half_rn(sum);
-                    if (lane < rows) g.y[row0 + lane] = hv;
-                    float v = lane < rows ? __half2float(hv) : -INFINITY;
-                    if (!(v == v)) v = -INFINITY;  // NaN never wins
-                    int idx = row0 + lane;
-                    for (int m = g.nr >> 1; m >= 1; m >>= 1) {
-                        const float ov = __shfl_xor_sync(mask, v, m);
-                        const int oi = __shfl_xor_sync(mask, idx, m);
-                        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
-                    }
-                    if (lane == 0 && (v > sh.best_val[grp] || (v == sh.best_val[grp] && idx < sh.best_idx[grp]))) {
-                        sh.best_val[grp] = v;
-                        sh.best_idx[grp] = idx;
-                    }
-                } else if (g.kind == PH_O || g.kind == PH_DOWN) {
-                    if (lane < rows) {
-                        const float o = __half2float(__float2half_rn(sum));
-                        // L2 load: other SMs wrote the residual stream earlier in this launch
-                        const __half out = __float2half_rn(o + __half2float(__ldcg(&g.res[row0 + lane])));
-                        g.y[row0 + lane] = out;
-                        if (g.hidden_row) g.hidden_row[row0 + lane] = out;
-                    }
-                } else {  // PH_QKV: RoPE on q and k rows, then q buffer / cache row `pos`
-                    const int row = row0 + lane;
-                    const float v = __half2float(__float2half_rn(sum));
-                    const float other = __shfl_xor_sync(mask, v, 1);
-                    if (lane < rows && pos >= 0 && pos < p.max_pos) {
-                        const DsLayer &L = p.layers[l];
-                        if (row < n_q + n_kv) {
-                            const int local = row < n_q ? row : row - n_q;
-                            const float2 cs = sh.rope_cs[(local >> 1) % (p.hd >> 1)];
-                            const float outv = (row & 1) ? __fmaf_rn(cs.y, other, __fmul_rn(cs.x, v))
-                                                         : __fmaf_rn(cs.x, v, -__fmul_rn(cs.y, other));
-                            const __half hv = __float2half_rn(outv);
-                            if (row < n_q) p.q[row] = hv;
-                            else L.k_cache[(size_t)pos * n_kv + local] = hv;
-                        } else {
-                            L.v_cache[(size_t)pos * n_kv + (row - n_q - n_kv)] = __float2half_rn(sum);
-                        }
-                    }
-                }
-            }
-        }
-        if (is_lm) {  // this CTA's best logit travels with the phase's arrival
-            named_bar_sync(3, kDsConsumers);
-            if (tid == 0) {
-                const bool second = sh.best_val[1] > sh.best_val[0] ||
-                                    (sh.best_val[1] == sh.best_val[0] && sh.best_idx[1] < sh.best_idx[0]);
-                p.amax_val[blockIdx.x] = sh.best_val[second ? 1 : 0];
-                p.amax_idx[blockIdx.x] = sh.best_idx[second ? 1 : 0];
+                if ((lane & ((32 / g.nr) - 1)) == 0) sh.red[s][my_row][gwarp] = tot;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.done_bar[s]);  // release: partials written, slot read
             }
         }
         grid_arrive();
         stamp(tphase, 3);
         ++tphase;
 
-        if (!is_lm && (ph & 3) == PH_QKV) {
+        if (g.kind == PH_QKV) {
+            const int l = ph >> 2;
             // ------------------------------ attention ------------------------------
             stamp(tphase, 0);
-            grid_wait();
-            stamp(tphase, 1);
-            const DsLayer &L = p.layers[l];
+            const DsLayer &L = layer_s[l];
             const int HD = p.hd;
             const int chunks = HD >> 3;
             const int len_total = pos + 1;
@@ -489,23 +510,37 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             int tpd = kDsConsumers / (kDsTile * G);  // threads per (row, head) dot product
             tpd = tpd < 1 ? 1 : (tpd > 4 ? 4 : tpd);
             const int n_out = G * HD;
+            auto load_rows = [&](int kvh, int t0, int r_begin, int r_end) {
+                for (int c = tid + r_begin * chunks; c < r_end * chunks; c += kDsConsumers) {
+                    const int r = c / chunks, ch = c % chunks;
+                    const size_t goff = (size_t)(t0 + r) * n_kv + (size_t)kvh * HD + ch * 8;
+                    cp_async16_ds(&k_tile[r * HD + ((ch ^ (r & 7)) * 8)], L.k_cache + goff);
+                    cp_async16_ds(&v_tile[r * HD + ch * 8], L.v_cache + goff);
+                }
+            };
+            // Cache rows below `pos` were written by earlier steps: the first tile of this CTA's first
+            // task is requested before waiting for the other CTAs' q/k/v rows of this step.
+            int pre_rows = 0;
+            if ((int)blockIdx.x < n_tasks) {
+                const int kvh = blockIdx.x / p.n_splits, begin = (blockIdx.x % p.n_splits) * p.split_len;
+                pre_rows = max(0, min(kDsTile, min(begin + p.split_len, pos) - begin));
+                load_rows(kvh, begin, 0, pre_rows);
+            }
+            grid_wait();
+            stamp(tphase, 1);
             for (int task = blockIdx.x; task < n_tasks && ok; task += gridDim.x) {
                 const int kvh = task / p.n_splits, split = task % p.n_splits;
                 const int begin = split * p.split_len;
                 const int end = min(begin + p.split_len, len_total);
-                named_bar_sync(1, kDsConsumers);
+                if (task != (int)blockIdx.x) named_bar_sync(1, kDsConsumers);  // previous task is done with shared memory
                 for (int i = tid; i < n_out; i += kDsConsumers) sh.q_s[i] = __half2float(__ldcg(&p.q[(size_t)kvh * n_out + i]));
                 if (tid < G) { sh.m_s[tid] = -INFINITY; sh.l_s[tid] = 0.0f; }
                 float acc[2] = {0.0f, 0.0f};
                 for (int t0 = begin; t0 < end; t0 += kDsTile) {
                     const int rows = min(kDsTile, end - t0);
-                    named_bar_sync(1, kDsConsumers);  // previous tile consumed; q_s visible
-                    for (int c = tid; c < rows * chunks; c += kDsConsumers) {
-                        const int r = c / chunks, ch = c % chunks;
-                        const size_t goff = (size_t)(t0 + r) * n_kv + (size_t)kvh * HD + ch * 8;
-                        cp_async16_ds(&k_tile[r * HD + ((ch ^ (r & 7)) * 8)], L.k_cache + goff);
-                        cp_async16_ds(&v_tile[r * HD + ch * 8], L.v_cache + goff);
-                    }
+                    const bool first = task == (int)blockIdx.x && t0 == begin;
+                    if (!first) named_bar_sync(1, kDsConsumers);  // previous tile consumed
+                    load_rows(kvh, t0, first ? pre_rows : 0, rows);
                     cp_async_wait_all_ds();
                     named_bar_sync(1, kDsConsumers);
                     // scores: dot = head * tile + row, split over tpd adjacent lanes
@@ -573,9 +608,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     const int o = tid + kDsConsumers * i;
                     if (o < n_out) p.part_o[(pbase + o / HD) * HD + (o % HD)] = acc[i];
                 }
-                __threadfence();
                 named_bar_sync(1, kDsConsumers);
                 if (tid == 0) {
+                    __threadfence();  // cumulative: orders the whole CTA's partials before the count
                     const int prev = atomicAdd(&p.attn_counters[kvh], 1);
                     sh.is_last = (prev == p.n_splits - 1);
                     if (sh.is_last) p.attn_counters[kvh] = 0;
@@ -583,24 +618,51 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 named_bar_sync(1, kDsConsumers);
                 if (sh.is_last) {
                     __threadfence();
+                    // Merge in split order.  All loads of a step are independent, so each step costs
+                    // about one L2 round trip: (1) every (split, head) max and sum, (2) the weights,
+                    // (3) the partial outputs in batches of eight splits.
                     const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
                     const size_t gbase = (size_t)kvh * p.n_splits * G;
+                    float *m_all = sh.norm_buf[0];  // idle during attention: [split][head]
+                    float *l_all = sh.norm_buf[1];
+                    for (int e = tid; e < n_used * G; e += kDsConsumers) {
+                        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(gbase + e) * 2]));
+                        m_all[e] = ml.x;
+                        l_all[e] = ml.y;
+                    }
+                    named_bar_sync(1, kDsConsumers);
+                    float wgt_keep = 0.0f;
+                    int e_keep = -1;
+                    if (tid < n_used * G && tid < 512) {
+                        const int hh = tid % G;
+                        float M = -INFINITY;
+                        for (int sidx = 0; sidx < n_used; ++sidx) M = fmaxf(M, m_all[sidx * G + hh]);
+                        const float m = m_all[tid];
+                        wgt_keep = (m == -INFINITY) ? 0.0f : expf(m - M);
+                        e_keep = tid;
+                    }
+                    named_bar_sync(1, kDsConsumers);
+                    if (e_keep >= 0) m_all[e_keep] = wgt_keep;  // m_all now holds the weights
+                    named_bar_sync(1, kDsConsumers);
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const int o = tid + kDsConsumers * i;
                         if (o < n_out) {
                             const int hh = o / HD, dd = o % HD;
-                            float M = -INFINITY;
-                            for (int sidx = 0; sidx < n_used; ++sidx)
-                                M = fmaxf(M, __ldcg(&p.part_ml[(gbase + (size_t)sidx * G + hh) * 2]));
                             float num = 0.0f, den = 0.0f;
-                            for (int sidx = 0; sidx < n_used; ++sidx) {
-                                const size_t pi = gbase + (size_t)sidx * G + hh;
-                                const float m = __ldcg(&p.part_ml[pi * 2]);
-                                const float lsum = __ldcg(&p.part_ml[pi * 2 + 1]);
-                                const float wgt = (m == -INFINITY) ? 0.0f : expf(m - M);
-                                num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + dd]), num);
-                                den = fmaf(wgt, lsum, den);
+                            for (int s0 = 0; s0 < n_used; s0 += 8) {
+                                float v[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    v[u] = (s0 + u < n_used) ? __ldcg(&p.part_o[(gbase + (size_t)(s0 + u) * G + hh) * HD + dd]) : 0.0f;
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    if (s0 + u < n_used) {
+                                        const float wgt = m_all[(s0 + u) * G + hh];
+                                        num = fmaf(wgt, v[u], num);
+                                        den = fmaf(wgt, l_all[(s0 + u) * G + hh], den);
+                                    }
+                                }
                             }
                             p.attn[(size_t)kvh * n_out + o] = __float2half_rn(__fdiv_rn(num, den));
                         }
@@ -666,6 +728,7 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
         a->split_len <= 0 || (a->split_len % kDsTile) != 0 || a->n_splits > a->max_splits)
         return LLMB_ERR_INVALID;
     const int G = a->n_q_heads / a->n_kv_heads;
+    if (a->n_splits * G > 512) return LLMB_ERR_INVALID;  // the merge keeps one weight per (split, head) in shared memory
     if ((a->head_dim != 64 && a->head_dim != 128) || G > 8 || G * a->head_dim > 2 * kDsConsumers) return LLMB_ERR_UNSUPPORTED;
     if (a->d_model % 8 || a->ffn % 8 || a->d_model > 8192 || a->ffn > 16384 || a->n_q_heads * a->head_dim > 16384)
         return LLMB_ERR_UNSUPPORTED;
@@ -722,11 +785,20 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
     p.with_logits = a->with_logits;
     p.history_len = a->history_len;
 
-    const size_t smem = (size_t)kDsSlots * kDsSlotBytes + (size_t)2 * kDsTile * 128 * sizeof(__half);
-    static bool attr_set = false;
-    if (!attr_set) {
+    const size_t smem = (size_t)kDsSlots * kDsSlotBytes + (size_t)2 * kDsTile * 128 * sizeof(__half) +
+                        (size_t)a->n_layers * sizeof(DsLayer);
+    static size_t smem_limit = 0, smem_set = 0;
+    if (!smem_limit) {
+        cudaFuncAttributes fa;
+        int optin = 0;
+        LLMB_CUDA_OK(cudaFuncGetAttributes(&fa, decode_step_kernel));
+        LLMB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        smem_limit = (size_t)optin > fa.sharedSizeBytes ? (size_t)optin - fa.sharedSizeBytes : 0;
+    }
+    if (smem > smem_limit) return LLMB_ERR_UNSUPPORTED;  // too many layers for the shared-memory table
+    if (smem > smem_set) {
         LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+        smem_set = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms);

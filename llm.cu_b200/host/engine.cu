@@ -195,7 +195,9 @@ int kernels_per_step(const Engine *e, bool with_logits) {
 int launch_step_kernel(Engine *e, bool with_logits, int len) {
     const Llama3Config &c = e->model->config;
     int split_len = 32;
-    while (e->nkv * ((len + split_len - 1) / split_len) > 2 * e->sm_count) split_len *= 2;
+    const int G = e->nq / e->nkv;
+    while (e->nkv * ((len + split_len - 1) / split_len) > 2 * e->sm_count || ((len + split_len - 1) / split_len) * G > 512)
+        split_len *= 2;
     LlmbDecodeStepArgs a = {};
     a.layers = e->d_layers;
     a.n_layers = e->layers;
