@@ -137,6 +137,19 @@ int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint1
                      int n_q_heads, int n_kv_heads, int head_dim, int n_splits, int split_len, uint16_t *d_out,
                      void *d_scratch, int use_pdl, llmb_stream_t stream);
 
+/* The same attention for callers that may not allocate device memory (a host whose own pool  */
+/* owns the device, a loop that cannot afford an allocation's synchronisation, a plug-in that  */
+/* only ever sees its input and output buffers): no workspace argument, the partial results     */
+/* live in a fixed 2,130,176-byte array inside the library.  No counterpart in the reference,   */
+/* which allocates every buffer with cudaMalloc in init_cache (inference.cu:101-145).           */
+/* Limits: n_q_heads * n_splits <= 4096, head_dim <= 128, n_kv_heads <= 64; larger requests     */
+/* return LLMB_ERR_UNSUPPORTED.  The first call on each device resolves the array's address and  */
+/* should be made before any stream capture begins.  Calls on one device share the array: calls */
+/* that may run concurrently on the GPU race.  Allocates nothing.                               */
+int llmb_attn_decode_static(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                            const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
+                            int split_len, uint16_t *d_out, int use_pdl, llmb_stream_t stream);
+
 /* ------------------------------------------------------------------------------------ */
 /* Greedy sampling on the device: index of the first maximum of n FP16 logits (NaN never   */
 /* wins).  Replaces the host sampler sample_next_token (inference.cu:1030-1161) for greedy */

@@ -24,7 +24,7 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step",
+    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
@@ -107,6 +107,7 @@ def _declare(l):
     l.llmb_attn_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.llmb_attn_decode_scratch_bytes.restype = sz
     l.llmb_attn_decode.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+    l.llmb_attn_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]
     l.llmb_argmax_f16.argtypes = [vp, i32, vp, vp, vp, i32, i32, vp]
     l.llmb_advance_pos.argtypes = [vp, i32, vp]
     M, K = C.POINTER(Llama3Struct), C.POINTER(CudaCacheStruct)

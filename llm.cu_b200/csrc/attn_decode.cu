@@ -16,6 +16,8 @@
 //   merge  each CTA writes (max, sum, unnormalised out) per query head to scratch; the last
 //          CTA to finish for a KV head (atomic counter) rescales and adds the partials in split
 //          order, normalises and writes FP16 (inference.cu:945).  The counter is left at zero.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace llmb {
@@ -277,4 +279,86 @@ extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, 
         }
     }
     return LLMB_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------
+// llmb_attn_decode_static: the same split-KV attention, for hosts that must not allocate.
+//
+// Some programs that embed this library cannot call cudaMalloc themselves: an inference
+// server that handed the whole device to its own pool at start-up and treats any later
+// driver allocation as a bug, a real-time loop that cannot take the device-wide
+// synchronisation an allocation may imply, or a plug-in that only receives input and output
+// buffers from its host and has nowhere to keep a workspace.  For them the partial results
+// live in the fixed array below instead of a caller-provided workspace.
+//
+//  * Limit: n_q_heads * n_splits <= 4096, head_dim <= 128, n_kv_heads <= 64; the array is
+//    2,130,176 bytes and every GPU that loads the library carries it until the process ends.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress:
+//    in host code the array's name is only a handle, not something a kernel can dereference)
+//    and remembers it; make that first call before starting any stream capture.
+//  * All calls on a device share the one array and it keeps whatever the previous call
+//    left, so the arrival counters are cleared on the stream before each launch; two calls
+//    that can overlap on the GPU (different streams, no dependency) race on it.
+//  * No cudaMalloc, cudaFree or allocating library routine is called.
+// ---------------------------------------------------------------------------------------
+namespace llmb {
+
+constexpr int kStaticMaxHeadSplits = 4096;  // n_q_heads * n_splits
+constexpr int kStaticMaxHeadDim = 128;
+constexpr int kStaticMaxKvHeads = 64;
+constexpr size_t kStaticCounterBytes = 256;
+constexpr size_t kStaticMlBytes = (size_t)kStaticMaxHeadSplits * 2 * sizeof(float);
+constexpr size_t kStaticScratchBytes =
+    kStaticCounterBytes + kStaticMlBytes + (size_t)kStaticMaxHeadSplits * kStaticMaxHeadDim * sizeof(float);
+
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+static std::mutex g_static_mu;
+static void *g_static_ptr[64] = {};
+
+// Device address of the array on the current device (looked up once per device).
+static int static_scratch_ptr(void **out) {
+    int dev = 0;
+    LLMB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_last_error("llmb_attn_decode_static: device ordinal above 63");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *ptr = nullptr;
+        LLMB_CUDA_OK(cudaGetSymbolAddress(&ptr, g_attn_static_scratch));
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return LLMB_OK;
+}
+
+}  // namespace llmb
+
+extern "C" int llmb_attn_decode_static(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                                       const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
+                                       int split_len, uint16_t *d_out, int use_pdl, llmb_stream_t stream_) {
+    using namespace llmb;
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_splits <= 0 || head_dim <= 0) return LLMB_ERR_INVALID;
+    if ((long long)n_q_heads * n_splits > kStaticMaxHeadSplits || head_dim > kStaticMaxHeadDim ||
+        n_kv_heads > kStaticMaxKvHeads) {
+        set_last_error(
+            "llmb_attn_decode_static: request exceeds the built-in workspace (n_q_heads * n_splits <= 4096, "
+            "head_dim <= 128, n_kv_heads <= 64); use llmb_attn_decode with a caller-provided workspace");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    void *scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    // Carve the array exactly as llmb_attn_decode carves a caller workspace of this request's size:
+    // the layout depends on the request, not on the array's capacity, and fits by the check above.
+    if (llmb_attn_decode_scratch_bytes(n_q_heads, n_kv_heads, head_dim, n_splits) > kStaticScratchBytes) {
+        set_last_error("llmb_attn_decode_static: request exceeds the built-in workspace");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    // The counters must start at zero; a finished call leaves them so, an interrupted one may not.
+    LLMB_CUDA_OK(cudaMemsetAsync(scratch, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream_)));
+    return llmb_attn_decode(d_q, d_k_cache, d_v_cache, d_pos, n_q_heads, n_kv_heads, head_dim, n_splits, split_len,
+                            d_out, scratch, use_pdl, stream_);
 }
