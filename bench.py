@@ -119,6 +119,8 @@ def run_ours(args):
     max_seq = max(2048, PROMPT + 2 * (W + K) + 8)
     model = pkg.Model.synthetic(cfg, seed=SEED, max_seq=max_seq)
     cache = pkg.Cache(model)
+    if args.per_op_kernels:
+        cache.set_options(step_kernel=0)
     # the prompt: uniform ids, the same stream the tests and the oracle use (seed + 1)
     import ctypes as C
     prompt = prompt_ids(cfg.vocab)
@@ -183,8 +185,10 @@ def run_ours(args):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": None, "peak_source": peak_src,
-                     "scope": "whole decode step (1 + 5*32 + 2 launches, dominated by the FP16 GEMV kernel); "
-                              "algorithmic bytes per step = weights 15,009,857,536 + 131,072 per cached row",
+                     "scope": ("whole decode step: one kernel per fused op, 163 launches in a CUDA graph" if args.per_op_kernels else
+                               "decode_step_kernel: one persistent launch per token") +
+                              "; algorithmic bytes per launch = weight bytes %d + %d per cached row" % (
+                                  cfg.weight_bytes_per_token(), cfg.kv_bytes_per_position()),
                      "algorithmic_bytes_per_step": alg_bytes},
         "tokens_match_e2e": toks[:8] == seq[PROMPT + 1 + max(W, 3):PROMPT + 1 + max(W, 3) + 8],
     }
@@ -298,6 +302,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-max-steps", type=int, default=6)
     ap.add_argument("--tmpdir", default=None)
+    ap.add_argument("--per-op-kernels", action="store_true", help="one kernel per fused op in a CUDA graph instead of the whole-step kernel")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="shorter prompts are for profiling runs only")
     args = ap.parse_args()
     PROMPT = args.prompt_len

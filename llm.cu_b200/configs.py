@@ -52,5 +52,7 @@ CONFIGS = {
     # 8B layer shape, two layers, small embedding table: small enough to run through the reference
     # binary and the CPU oracle in seconds; used to pin the oracle against the reference itself
     "llama3_8b_l2": ModelConfig("llama3_8b_l2", 2, 4096, 32, 8, 128, 14336, 128256, embed_rows=1024),
+    # 8B layer shape cut down to ~2.3 GB (4 layers, 32K vocabulary) for multi-pass profiler captures
+    "llama3_8b_prof": ModelConfig("llama3_8b_prof", 4, 4096, 32, 8, 128, 14336, 32768),
     "llama3_70b": ModelConfig("llama3_70b", 80, 8192, 64, 8, 128, 28672, 128256),
 }
