@@ -130,6 +130,11 @@ int inference(Llama3 *llama3_model, Tensor *X, int *d_tokens, int *h_tokens, Cud
 int llama3_set_config(Llama3 *m, const Llama3Config *cfg); /* fields <= 0 keep their default */
 int llama3_set_tp(Llama3 *m, int tp_rank, int tp_size);
 int llama3_load_safetensors(Llama3 *m, const char *filename);
+/* The window {row0, rows, col0, cols, full_cols} of a loaded tensor that this model's
+ * tensor-parallel rank keeps: q/k/v, gate/up and lm_head split by rows, o_proj and down_proj by
+ * columns, everything else whole.  layer = -1, slot 1/2/3 = embed_tokens/lm_head/norm; otherwise
+ * slot is the position of the tensor in Llama3Layer (0 = input_layernorm ... 8 = v_proj). */
+int llama3_tensor_shard(Llama3 *m, int layer, int slot, int out[5]);
 int llama3_to_cuda(Llama3 *m);
 /* Random-init model written directly in device memory with the seeded generator of
  * llm_b200_synth.h (std 0.02, norm gains 1.0), BF16 then converted by the load-time kernel
@@ -147,6 +152,17 @@ int cache_set_options(CudaCache *cache, int use_graph, int use_pdl, int copy_log
  * = one persistent kernel per token (llmb_decode_step); 0 = one kernel per fused operation,
  * captured into a CUDA graph (llmb_gemv_f16, llmb_attn_decode, ...). */
 int cache_use_step_kernel(CudaCache *cache, int enable);
+/* Tensor parallel decode, one process per GPU (llama3_set_tp before loading): each rank exports a
+ * 64-byte CUDA IPC handle of its exchange block with cache_tp_handle(); the caller gathers all
+ * ranks' handles in rank order (torch.distributed, MPI, ...) and passes the tp_size * 64 bytes to
+ * cache_tp_connect().  Every rank then calls inference()/inference_greedy() with the same tokens.
+ * Cache->d_token_probdist / h_token_probdist hold this rank's slice of the vocabulary
+ * (rows [rank * vocab / tp_size, (rank + 1) * vocab / tp_size)).
+ * The ranks wait for one another inside the step kernel with a bounded spin of a few seconds; a
+ * rank that enters a step much later than its peers makes them give up (llmb_device_status 205),
+ * so keep the ranks in lock-step on the host (a barrier after any long rank-local work). */
+int cache_tp_handle(CudaCache *cache, void *handle_out /* 64 bytes */);
+int cache_tp_connect(CudaCache *cache, const void *handles /* tp_size * 64 bytes */);
 /* When enabled, every decode step also copies the residual stream after the embedding and
  * after each layer into an [n_layers + 1][d_model] FP16 device buffer (disables the graph). */
 int cache_enable_hidden_dump(CudaCache *cache, int enable);
@@ -160,6 +176,9 @@ int inference_greedy(Llama3 *m, CudaCache *cache, const int *prompt, int n_promp
  * inference_continue) left: the last sampled token is fed back on the device.  out_tokens[n_steps];
  * ms (optional) is the CUDA-event time of the n_steps steps. */
 int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int *out_tokens, float *ms);
+/* Test aid: copies an internal device buffer to the host (0 = residual row x, 1 = second residual
+ * buffer, 2 = q, 3 = attention output, 4 = SwiGLU output h, 5 = this rank's exchange block). */
+int cache_debug_read(CudaCache *cache, int which, void *out, size_t bytes);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

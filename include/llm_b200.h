@@ -54,6 +54,10 @@ int llmb_synth_bf16(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, uin
                     llmb_stream_t stream);
 int llmb_synth_fp16(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, uint64_t first, uint64_t n,
                     llmb_stream_t stream);
+/* A rows x cols window of a stream: out[r][c] = element first + r * row_stride + c, so that a
+ * tensor-parallel shard of a seeded tensor has the same bits as that slice of the whole tensor. */
+int llmb_synth_2d(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, int bf16, uint64_t first, uint64_t row_stride,
+                  uint64_t rows, uint64_t cols, llmb_stream_t stream);
 int llmb_fill_u16(uint16_t *d_out, uint16_t value, uint64_t n, llmb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------ */
@@ -205,12 +209,24 @@ typedef struct {
     int n_splits, split_len;
     int with_logits;
     uint16_t *hidden;       /* optional [n_layers + 1][d_model]: residual stream after each layer */
+    /* Tensor parallel (tp_size > 1): n_q_heads, n_kv_heads, ffn and vocab above are this rank's
+     * shares (q/k/v, gate/up, lm_head split by rows; o_proj, down_proj by columns; KV cache by KV
+     * head).  After o_proj and down_proj each rank stores its FP32 partial sums straight into every
+     * rank's exchange block over NVLink, the ranks synchronise through flags in those blocks, and
+     * every rank forms x = half(half(sum of partials) + x_old) itself: the all-reduce is part of
+     * the kernel.  peers[r] = device address, valid on this GPU, of rank r's exchange block of
+     * llmb_decode_step_exchange_bytes() bytes (zeroed once; own block at peers[tp_rank]).
+     * logits then hold this rank's vocabulary slice; next_token is the same on every rank. */
+    int tp_rank, tp_size, vocab_offset;
+    uint16_t *x_alt;        /* [d_model] second residual buffer */
+    void *peers[8];
     uint64_t *trace;        /* optional profiling aid, device [SM count][5 * n_layers + 2][4] nanosecond
                                stamps, one row per CTA; per phase: entered, dependency met, input ready,
                                done.  NULL in production. */
 } LlmbDecodeStepArgs;
 
 size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits);
+size_t llmb_decode_step_exchange_bytes(int tp_size, int d_model);
 int llmb_decode_step(const LlmbDecodeStepArgs *args, llmb_stream_t stream);
 
 #ifdef __cplusplus

@@ -23,14 +23,14 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
 # Symbols include/llm_b200.h and include/llama3.h declare; tests check each is exported.
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
-    "llmb_synth_fp16", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step",
+    "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
+    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
-    "llama3_to_cuda", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
-    "cache_set_options", "cache_use_step_kernel", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue",
+    "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
+    "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read",
     "cache_kernel_launches",
 ]
 
@@ -101,6 +101,7 @@ def _declare(l):
     l.llmb_bf16_to_fp16.argtypes = [vp, vp, sz, vp]
     l.llmb_synth_bf16.argtypes = [vp, u64, u64, C.c_float, u64, u64, vp]
     l.llmb_synth_fp16.argtypes = [vp, u64, u64, C.c_float, u64, u64, vp]
+    l.llmb_synth_2d.argtypes = [vp, u64, u64, C.c_float, i32, u64, u64, u64, u64, vp]
     l.llmb_fill_u16.argtypes = [vp, C.c_uint16, u64, vp]
     l.llmb_embed_rope.argtypes = [vp, vp, vp, i32, i32, i32, i32, C.c_float, vp, vp, i32, i32, vp]
     l.llmb_gemv_f16.argtypes = [C.POINTER(GemvArgs), vp]
@@ -130,6 +131,7 @@ def _declare(l):
     l.llama3_set_tp.argtypes = [M, i32, i32]
     l.llama3_load_safetensors.argtypes = [M, C.c_char_p]
     l.llama3_to_cuda.argtypes = [M]
+    l.llama3_tensor_shard.argtypes = [M, i32, i32, C.POINTER(C.c_int)]
     l.llama3_synth_weights.argtypes = [M, C.POINTER(Llama3Config), u64, i32]
     l.llama3_init_cache.argtypes = [M, C.POINTER(C.c_int)]
     l.llama3_init_cache.restype = K
@@ -138,6 +140,10 @@ def _declare(l):
     l.cache_reset.argtypes = [K]
     l.cache_set_options.argtypes = [K, i32, i32, i32]
     l.cache_use_step_kernel.argtypes = [K, i32]
+    l.cache_tp_handle.argtypes = [K, vp]
+    l.cache_tp_connect.argtypes = [K, vp]
+    l.llmb_decode_step_exchange_bytes.argtypes = [i32, i32]
+    l.llmb_decode_step_exchange_bytes.restype = sz
     l.cache_enable_hidden_dump.argtypes = [K, i32]
     l.llmb_decode_step_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.llmb_decode_step_scratch_bytes.restype = sz
@@ -146,6 +152,7 @@ def _declare(l):
     l.inference_greedy.argtypes = [M, K, C.POINTER(C.c_int), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_float),
                                    C.POINTER(C.c_float)]
     l.inference_continue.argtypes = [M, K, i32, C.POINTER(C.c_int), C.POINTER(C.c_float)]
+    l.cache_debug_read.argtypes = [K, i32, vp, sz]
     l.cache_kernel_launches.argtypes = [K]
     l.cache_kernel_launches.restype = C.c_longlong
 

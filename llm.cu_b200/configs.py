@@ -30,18 +30,20 @@ class ModelConfig:
             + 3 * self.ffn * self.d_model
         return per_layer * self.n_layers
 
-    def weight_bytes_per_token(self):
-        """Bytes of weights one decoded token must stream: projections, lm_head, norm gains, one
+    def weight_bytes_per_token(self, tp=1):
+        """Bytes of weights one decoded token must stream on each of `tp` tensor-parallel GPUs:
+        its share of the projections and of lm_head, plus the replicated norm gains and one
         embedding row."""
         norms = (2 * self.n_layers + 1) * self.d_model
-        return 2 * (self.matmul_params() + self.vocab * self.d_model + norms) + 2 * self.d_model
+        return 2 * ((self.matmul_params() + self.vocab * self.d_model) // tp + norms) + 2 * self.d_model
 
     def kv_bytes_per_position(self):
         return 2 * 2 * self.kv_rows * self.n_layers
 
-    def decode_bytes(self, cached_positions):
-        """Algorithmic bytes of one decode step that attends over `cached_positions` rows and appends one."""
-        return self.weight_bytes_per_token() + self.kv_bytes_per_position() * (cached_positions + 1)
+    def decode_bytes(self, cached_positions, tp=1):
+        """Algorithmic bytes, per GPU, of one decode step that attends over `cached_positions` rows and
+        appends one (the KV cache is split by KV head across `tp` GPUs)."""
+        return self.weight_bytes_per_token(tp) + self.kv_bytes_per_position() // tp * (cached_positions + 1)
 
 
 CONFIGS = {

@@ -73,7 +73,18 @@ struct DsParams {
     float rope_theta;
     int n_layers, d, nq, nkv, hd, ffn, vocab, embed_rows, max_pos;
     int n_splits, split_len, with_logits, history_len;
+    // tensor parallel: nq, nkv, ffn and vocab above are this rank's shares
+    int tp_rank, tp_size, vocab_offset;
+    __half *x_alt;              // second residual-stream buffer (ping-pong across all-reduces)
+    unsigned char *peer[8];     // every rank's exchange block (own block at [tp_rank]); see TpBlock
 };
+
+// Layout of a rank's exchange block, written by its peers over NVLink:
+//   [0, 64)      flags[r]  u64: highest synchronisation number rank r has announced
+//   [128, 136)   this rank's own count of synchronisations so far (local, persists across launches)
+//   [256, 512)   best[r]   (float value, int index): rank r's best logit of this step
+//   [512, ...)   recv[2][tp_size][d_model] FP32: partial projection sums, double-buffered
+constexpr size_t kTpFlagsOff = 0, kTpBestOff = 256, kTpRecvOff = 512;
 
 enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
 
@@ -81,6 +92,12 @@ struct GemvDesc {
     const __half *w, *w2, *x, *gamma, *res;
     __half *y, *hidden_row, *k_cache, *v_cache;
     int n, k, nr, R, kind;
+    // tensor parallel: `reduce` >= 0 means the input row is x_old + sum over ranks of recv[reduce & 1]
+    // (all-reduce number `reduce` of the step); `scatter` >= 0 means the output is a partial sum that
+    // goes to every rank's recv[scatter & 1] instead of the residual stream.
+    int reduce, scatter;
+    const __half *x_old;
+    __half *x_new;
 };
 
 __device__ __forceinline__ int rows_per_stage(int k) {
@@ -100,6 +117,9 @@ __device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, const DsLayer *
     g.res = nullptr;
     g.hidden_row = nullptr;
     g.k_cache = g.v_cache = nullptr;
+    g.reduce = g.scatter = -1;
+    g.x_old = nullptr;
+    g.x_new = nullptr;
     const int nq = p.nq * p.hd, nkv = p.nkv * p.hd;
     if (kind == PH_LM) {
         g.w = p.lm_head; g.x = p.x; g.gamma = p.g_final; g.y = p.logits; g.n = p.vocab; g.k = p.d;
@@ -115,6 +135,23 @@ __device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, const DsLayer *
         } else {
             g.w = L.wdown; g.x = p.h; g.res = p.x; g.y = p.x; g.n = p.d; g.k = p.ffn;
             if (p.hidden) g.hidden_row = p.hidden + (size_t)(l + 1) * p.d;
+        }
+    }
+    if (p.tp_size > 1) {
+        // all-reduce 2l follows o_proj of layer l, 2l + 1 follows its down_proj; the reduced row lands
+        // in residual buffer (number & 1), the previous row is in the other one (or the embedding)
+        __half *xb[2] = {p.x, p.x_alt};
+        if (kind == PH_O) g.scatter = 2 * l;
+        else if (kind == PH_DOWN) g.scatter = 2 * l + 1;
+        else if (kind == PH_GU) g.reduce = 2 * l;
+        else if (kind == PH_QKV && l > 0) g.reduce = 2 * l - 1;
+        else if (kind == PH_LM) g.reduce = 2 * p.n_layers - 1;
+        if (g.reduce >= 0) {
+            g.x_old = g.reduce == 0 ? emb : xb[(g.reduce - 1) & 1];
+            g.x_new = xb[g.reduce & 1];
+            g.hidden_row = (p.hidden && (g.reduce & 1)) ? p.hidden + (size_t)((g.reduce >> 1) + 1) * p.d : nullptr;
+        } else if (g.scatter >= 0) {
+            g.hidden_row = nullptr;
         }
     }
     g.nr = rows_per_stage(g.k);
@@ -246,10 +283,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     bool ok = true;                // only changes right after a barrier of all 17 warps
 
     // End of a phase for this CTA: all its global writes are ordered before the arrival.
+    // the cross-GPU synchronisation number lives in this rank's exchange block (never reset locally)
+    unsigned long long *tp_state = p.tp_size > 1 ? reinterpret_cast<unsigned long long *>(p.peer[p.tp_rank] + 128) : nullptr;
+    const unsigned long long tp_base = tp_state ? *tp_state : 0ULL;
+    unsigned long long n_tp = 0;   // cross-GPU synchronisations passed in this launch
     auto grid_arrive = [&]() {
         named_bar_sync(3, kDsThreads);
         if (tid == 0) {
-            __threadfence();
+            if (p.tp_size > 1) __threadfence_system();  // partial sums were stored into the peers' memory
+            else __threadfence();
             atomicAdd(p.bar, 1ULL);
         }
     };
@@ -269,6 +311,49 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         named_bar_sync(3, kDsThreads);
         if (sh.abort_flag) ok = false;
     };
+    // All ranks have finished the phase: the local wait, then CTA 0 announces it to the peers and
+    // every CTA waits until each peer has announced the same synchronisation number.
+    auto grid_wait_all_ranks = [&]() {
+        ++n_bar;
+        ++n_tp;
+        if (tid == 0 && ok) {
+            const unsigned long long target = bar_base + n_bar * (unsigned long long)gridDim.x;
+            const unsigned long long seq = tp_base + n_tp;
+            uint32_t polls = 0;
+            bool fine = true;
+            while (ld_acquire_u64(p.bar) < target) {
+                if (++polls > kPollLimit) { fine = false; break; }
+            }
+            if (fine && blockIdx.x == 0) {
+                __threadfence_system();
+                for (int r = 0; r < p.tp_size; ++r)
+                    if (r != p.tp_rank)
+                        *reinterpret_cast<volatile unsigned long long *>(p.peer[r] + kTpFlagsOff + 8 * p.tp_rank) = seq;
+            }
+            for (int r = 0; r < p.tp_size && fine; ++r) {
+                if (r == p.tp_rank) continue;
+                const unsigned long long *f = reinterpret_cast<const unsigned long long *>(p.peer[p.tp_rank] + kTpFlagsOff + 8 * r);
+                unsigned long long v;
+                polls = 0;
+                do {
+                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+                    if (++polls > kPollLimit) { fine = false; break; }
+                } while (v < seq);
+            }
+            if (!fine) {
+                atomicExch(p.status, 205);
+                sh.abort_flag = 1;
+            }
+        }
+        named_bar_sync(3, kDsThreads);
+        if (sh.abort_flag) ok = false;
+    };
+    // the wait that follows projection `ph`: across ranks where its output is an all-reduced sum
+    auto wait_after = [&](int prev_ph) {
+        const int kind = (prev_ph < 4 * p.n_layers) ? (prev_ph & 3) : PH_LM;
+        if (p.tp_size > 1 && (kind == PH_O || kind == PH_DOWN)) grid_wait_all_ranks();
+        else grid_wait();
+    };
 
     if (warp == kDsWarps) {
         // =========================== stage finisher ===========================
@@ -287,12 +372,12 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         uint32_t it = 0;
         for (int ph = 0; ph < n_gemv; ++ph) {
             const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
-            if (ph > 0) grid_wait();
+            if (ph > 0) wait_after(ph - 1);
             int gb, ge;
             cta_range((g.n + g.R - 1) / g.R, gb, ge);
             const unsigned mask = (1u << g.nr) - 1u;
             // Residual rows of this CTA: one batch of L2 loads per phase, not one round trip per stage.
-            const int res_rows = g.res ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
+            const int res_rows = (g.res && g.scatter < 0) ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
             const bool res_cached = res_rows <= 128;
             if (res_cached) {
                 for (int i = lane; i < res_rows; i += 32) sh.res_s[i] = __half2float(__ldcg(&g.res[gb * g.R + i]));
@@ -327,7 +412,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                             const int oi = __shfl_xor_sync(mask, idx, m);
                             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
                         }
+                        idx += p.vocab_offset;  // tensor parallel: this rank holds a slice of the vocabulary
                         if (v > best_val || (v == best_val && idx < best_idx)) { best_val = v; best_idx = idx; }
+                    } else if (g.scatter >= 0) {
+                        // tensor parallel: this rank's partial sum goes to every rank's receive buffer
+                        if (lane < rows) {
+                            const size_t off = kTpRecvOff + (((size_t)(g.scatter & 1) * p.tp_size + p.tp_rank) * p.d + row0 + lane) * 4;
+                            for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<float *>(p.peer[r] + off) = sum;
+                        }
                     } else if (g.kind == PH_O || g.kind == PH_DOWN) {
                         if (lane < rows) {
                             const float o = __half2float(__float2half_rn(sum));
@@ -358,6 +450,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 // slot s is free (all 8 warps have read it) and its partials are consumed: refill
                 if (lane == 0 && got) issue_next_stage(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
             }
+            // Stores into the peers' memory are posted over NVLink: the warp that issued them waits for
+            // them itself, a fence by another thread after a CTA barrier does not cover them.
+            if (g.scatter >= 0) __threadfence_system();
             if (g.kind == PH_LM && lane == 0) {  // this CTA's best logit travels with the phase's arrival
                 p.amax_val[blockIdx.x] = best_val;
                 p.amax_idx[blockIdx.x] = best_idx;
@@ -368,7 +463,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 grid_arrive();
             }
         }
-        grid_wait();
+        wait_after(n_gemv - 1);
         return;
     }
 
@@ -408,7 +503,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 if (have[j])
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4 *>(g.gamma) + gtid + kDsGThreads * j));
         }
-        if (ph > 0) grid_wait();  // the phase that produced x has finished everywhere
+        if (ph > 0) wait_after(ph - 1);  // the phase that produced x has finished everywhere
         stamp(tphase, 1);
 
         // Both groups hold the whole input row in registers (packed FP16): thread t of a group owns
@@ -416,9 +511,51 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         constexpr int kNormJ = kDsJ / 2;  // normalised inputs have k = d_model <= 8192
         uint4 xh[kDsJ];
         uint4 gv[kNormJ];
+        if (g.reduce < 0) {
 #pragma unroll
-        for (int j = 0; j < kDsJ; ++j)
-            xh[j] = have[j] ? __ldcg(reinterpret_cast<const uint4 *>(g.x) + gtid + kDsGThreads * j) : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < kDsJ; ++j)
+                xh[j] = have[j] ? __ldcg(reinterpret_cast<const uint4 *>(g.x) + gtid + kDsGThreads * j) : make_uint4(0, 0, 0, 0);
+        } else {
+            // Tensor parallel: the input row is the all-reduced projection plus the previous residual
+            // row, x = half(float(half(sum over ranks of partials)) + float(x_old)): the reference's
+            // rounding points (inference.cu:445, :385-387) with the sum taken in rank order.  Every CTA
+            // forms the whole row for itself; the chunk's owner CTA also stores it for later residual adds.
+            const float *recv = reinterpret_cast<const float *>(p.peer[p.tp_rank] + kTpRecvOff) +
+                                (size_t)(g.reduce & 1) * p.tp_size * p.d;
+#pragma unroll
+            for (int j = 0; j < kDsJ / 2; ++j) {
+                xh[j] = make_uint4(0, 0, 0, 0);
+                if (have[j]) {
+                    const int c = gtid + kDsGThreads * j;
+                    float acc8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc8[e] = 0.0f;
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        const float4 a = __ldcg(reinterpret_cast<const float4 *>(recv + (size_t)r * p.d + c * 8));
+                        const float4 b = __ldcg(reinterpret_cast<const float4 *>(recv + (size_t)r * p.d + c * 8 + 4));
+                        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
+                        acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+                    }
+                    const uint4 xo = __ldcg(reinterpret_cast<const uint4 *>(g.x_old) + c);
+                    float xf[8];
+                    unpack8(xo, xf);
+                    uint4 xn;
+                    __half2 *o = reinterpret_cast<__half2 *>(&xn);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        o[e] = __halves2half2(
+                            __float2half_rn(__half2float(__float2half_rn(acc8[2 * e])) + xf[2 * e]),
+                            __float2half_rn(__half2float(__float2half_rn(acc8[2 * e + 1])) + xf[2 * e + 1]));
+                    xh[j] = xn;
+                    if (grp == 0 && (c % (int)gridDim.x) == (int)blockIdx.x) {
+                        reinterpret_cast<uint4 *>(g.x_new)[c] = xn;
+                        if (g.hidden_row) reinterpret_cast<uint4 *>(g.hidden_row)[c] = xn;
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = kDsJ / 2; j < kDsJ; ++j) xh[j] = make_uint4(0, 0, 0, 0);
+        }
         if (g.gamma) {
 #pragma unroll
             for (int j = 0; j < kNormJ; ++j)
@@ -677,7 +814,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     }
 
     // ---- step epilogue ----
-    grid_wait();  // every CTA has finished its last phase (and published its best logit)
+    wait_after(n_gemv - 1);  // every CTA has finished its last phase (and published its best logit)
     if (blockIdx.x == 0 && warp == 0) {
         int token = -1;
         if (p.with_logits) {
@@ -694,6 +831,42 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 const int oi = __shfl_xor_sync(0xffffffffu, idx, m);
                 if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
             }
+            if (p.tp_size > 1) {
+                // each rank's best logit goes to every rank; then one more announcement round
+                if (lane == 0) {
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        volatile float *bv = reinterpret_cast<volatile float *>(p.peer[r] + kTpBestOff + 8 * p.tp_rank);
+                        bv[0] = v;
+                        reinterpret_cast<volatile int *>(bv)[1] = idx;
+                    }
+                    __threadfence_system();
+                    const unsigned long long seq = tp_base + (++n_tp);
+                    for (int r = 0; r < p.tp_size; ++r)
+                        if (r != p.tp_rank)
+                            *reinterpret_cast<volatile unsigned long long *>(p.peer[r] + kTpFlagsOff + 8 * p.tp_rank) = seq;
+                    bool fine = true;
+                    for (int r = 0; r < p.tp_size && fine; ++r) {
+                        if (r == p.tp_rank) continue;
+                        const unsigned long long *f = reinterpret_cast<const unsigned long long *>(p.peer[p.tp_rank] + kTpFlagsOff + 8 * r);
+                        unsigned long long fv;
+                        uint32_t polls = 0;
+                        do {
+                            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(fv) : "l"(f) : "memory");
+                            if (++polls > kPollLimit) { fine = false; break; }
+                        } while (fv < seq);
+                    }
+                    if (!fine) atomicExch(p.status, 206);
+                    v = -INFINITY;
+                    idx = 0x7fffffff;
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        const volatile float *bv = reinterpret_cast<const volatile float *>(p.peer[p.tp_rank] + kTpBestOff + 8 * r);
+                        const float ov = bv[0];
+                        const int oi = reinterpret_cast<const volatile int *>(bv)[1];
+                        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+                    }
+                }
+                idx = __shfl_sync(0xffffffffu, idx, 0);
+            }
             token = idx == 0x7fffffff ? 0 : idx;
         }
         if (lane == 0) {
@@ -704,6 +877,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             }
             *p.pos = np;
             p.bar[1] = bar_base + n_bar * (unsigned long long)gridDim.x;
+            if (tp_state) *tp_state = tp_base + n_tp;
         }
     }
 }
@@ -713,6 +887,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
 using namespace llmb;
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t llmb_decode_step_exchange_bytes(int tp_size, int d_model) {
+    if (tp_size < 1 || d_model <= 0) return 0;
+    return kTpRecvOff + (size_t)2 * tp_size * d_model * sizeof(float);
+}
 
 extern "C" size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {
     if (n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_splits <= 0) return 0;
@@ -784,6 +963,21 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
     p.split_len = a->split_len;
     p.with_logits = a->with_logits;
     p.history_len = a->history_len;
+    p.tp_rank = 0;
+    p.tp_size = 1;
+    p.vocab_offset = 0;
+    p.x_alt = nullptr;
+    if (a->tp_size > 1) {
+        if (a->tp_size > 8 || a->tp_rank < 0 || a->tp_rank >= a->tp_size || !a->x_alt) return LLMB_ERR_INVALID;
+        for (int r = 0; r < a->tp_size; ++r) {
+            if (!a->peers[r]) return LLMB_ERR_INVALID;
+            p.peer[r] = static_cast<unsigned char *>(a->peers[r]);
+        }
+        p.tp_rank = a->tp_rank;
+        p.tp_size = a->tp_size;
+        p.vocab_offset = a->vocab_offset;
+        p.x_alt = reinterpret_cast<__half *>(a->x_alt);
+    }
 
     const size_t smem = (size_t)kDsSlots * kDsSlotBytes + (size_t)2 * kDsTile * 128 * sizeof(__half) +
                         (size_t)a->n_layers * sizeof(DsLayer);

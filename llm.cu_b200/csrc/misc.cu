@@ -50,6 +50,18 @@ __global__ void synth_kernel(uint16_t *out, uint64_t key, float std, uint64_t fi
         out[i] = BF16 ? llmb_synth_bf16(key, first + i, std) : llmb_synth_fp16(key, first + i, std);
 }
 
+// 2-D window of a stream: out[r][c] = element first + r * row_stride + c (tensor-parallel shards).
+template <bool BF16>
+__global__ void synth_2d_kernel(uint16_t *out, uint64_t key, float std, uint64_t first, uint64_t row_stride, uint64_t rows,
+                                uint64_t cols) {
+    const uint64_t n = rows * cols;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint64_t src = first + (i / cols) * row_stride + (i % cols);
+        out[i] = BF16 ? llmb_synth_bf16(key, src, std) : llmb_synth_fp16(key, src, std);
+    }
+}
+
 __global__ void fill_u16_kernel(uint16_t *out, uint16_t value, uint64_t n) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = value;
@@ -199,6 +211,18 @@ extern "C" int llmb_synth_fp16(uint16_t *d_out, uint64_t seed, uint64_t sid, flo
     if (n == 0) return LLMB_OK;
     synth_kernel<false><<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
         d_out, llmb_stream_key(seed, sid), std, first, n);
+    LLMB_CUDA_OK(cudaGetLastError());
+    return LLMB_OK;
+}
+
+extern "C" int llmb_synth_2d(uint16_t *d_out, uint64_t seed, uint64_t sid, float std, int bf16, uint64_t first,
+                             uint64_t row_stride, uint64_t rows, uint64_t cols, llmb_stream_t stream_) {
+    if (!d_out) return LLMB_ERR_INVALID;
+    if (rows == 0 || cols == 0) return LLMB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    const uint64_t key = llmb_stream_key(seed, sid);
+    if (bf16) synth_2d_kernel<true><<<grid_for(rows * cols, 256), 256, 0, st>>>(d_out, key, std, first, row_stride, rows, cols);
+    else synth_2d_kernel<false><<<grid_for(rows * cols, 256), 256, 0, st>>>(d_out, key, std, first, row_stride, rows, cols);
     LLMB_CUDA_OK(cudaGetLastError());
     return LLMB_OK;
 }

@@ -21,8 +21,10 @@ class Model:
             raise MemoryError("init_llama3 failed")
 
     @classmethod
-    def from_safetensors(cls, cfg, paths, max_seq=2048):
+    def from_safetensors(cls, cfg, paths, max_seq=2048, tp_rank=0, tp_size=1):
         m = cls(cfg.n_layers)
+        if tp_size > 1:
+            check(lib.llama3_set_tp(m.ptr, tp_rank, tp_size), "llama3_set_tp")
         partial = Llama3Config(0, 0, 0, cfg.head_dim, 0, 0, max_seq, cfg.rope_theta, cfg.eps)
         check(lib.llama3_set_config(m.ptr, C.byref(partial)), "llama3_set_config")
         for p in paths:
@@ -31,8 +33,10 @@ class Model:
         return m
 
     @classmethod
-    def synthetic(cls, cfg, seed=0, max_seq=2048):
+    def synthetic(cls, cfg, seed=0, max_seq=2048, tp_rank=0, tp_size=1):
         m = cls(cfg.n_layers)
+        if tp_size > 1:
+            check(lib.llama3_set_tp(m.ptr, tp_rank, tp_size), "llama3_set_tp")
         c = _cfg_struct(cfg, max_seq)
         check(lib.llama3_synth_weights(m.ptr, C.byref(c), seed, 1 if cfg.bf16_weights else 0), "llama3_synth_weights")
         return m
@@ -64,7 +68,9 @@ class Cache:
         self.ptr = lib.llama3_init_cache(model.ptr, C.byref(rc))
         if not self.ptr:
             check(rc.value or 1, "init_cache")
-        self.vocab = model.config.vocab
+        self.tp_size = model.ptr.contents.tp_size
+        self.tp_rank = model.ptr.contents.tp_rank
+        self.vocab = model.config.vocab // self.tp_size  # this rank's slice of the logits
         self.max_seq = model.config.max_seq
         self._tokens = (C.c_int * (self.max_seq + 2))()
         self._x = TensorStruct()
@@ -74,6 +80,24 @@ class Cache:
         check(lib.cache_set_options(self.ptr, int(use_graph), int(use_pdl), int(copy_logits)), "cache_set_options")
         if step_kernel >= 0:
             check(lib.cache_use_step_kernel(self.ptr, int(step_kernel)), "cache_use_step_kernel")
+
+    def tp_connect(self, group=None):
+        """Exchanges the CUDA IPC handles of the ranks' exchange blocks over torch.distributed and maps the
+        peers' blocks (one process per GPU; every rank calls this once before the first step)."""
+        import torch
+        import torch.distributed as dist
+        mine = (C.c_ubyte * 64)()
+        check(lib.cache_tp_handle(self.ptr, mine), "cache_tp_handle")
+        t = torch.tensor(list(bytes(mine)), dtype=torch.uint8)
+        use_cuda = dist.get_backend(group) == "nccl"
+        if use_cuda:
+            t = t.cuda()
+        out = [torch.empty_like(t) for _ in range(self.tp_size)]
+        dist.all_gather(out, t, group=group)
+        blob = b"".join(bytes(o.cpu().tolist()) for o in out)
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        check(lib.cache_tp_connect(self.ptr, buf), "cache_tp_connect")
+        dist.barrier(group=group)
 
     def reset(self):
         check(lib.cache_reset(self.ptr), "cache_reset")

@@ -58,6 +58,13 @@ struct Engine {
     int step_max_splits = 0;
     int sm_count = 148;
     bool use_step_kernel = true;
+    // tensor parallel
+    int tp_rank = 0, tp_size = 1;
+    __half *x_alt = nullptr;
+    void *exchange = nullptr;           // this rank's exchange block (peers write into it)
+    size_t exchange_bytes = 0;
+    void *peers[8] = {};                // every rank's block as mapped on this device
+    bool tp_connected = false;
     int *h_next = nullptr;  // pinned
     __half *hidden = nullptr;
     bool use_graph = true, use_pdl = true, copy_logits = true, hidden_dump = false;
@@ -229,6 +236,17 @@ int launch_step_kernel(Engine *e, bool with_logits, int len) {
     a.n_splits = (len + split_len - 1) / split_len;
     a.with_logits = with_logits ? 1 : 0;
     a.hidden = e->hidden_dump ? reinterpret_cast<uint16_t *>(e->hidden) : nullptr;
+    if (e->tp_size > 1) {
+        if (!e->tp_connected) {
+            set_last_error("tensor parallel cache: call cache_tp_connect() on every rank first");
+            return LLMB_ERR_INVALID;
+        }
+        a.tp_rank = e->tp_rank;
+        a.tp_size = e->tp_size;
+        a.vocab_offset = e->tp_rank * e->vocab;
+        a.x_alt = reinterpret_cast<uint16_t *>(e->x_alt);
+        for (int r = 0; r < e->tp_size; ++r) a.peers[r] = e->peers[r];
+    }
     return llmb_decode_step(&a, e->stream);
 }
 
@@ -288,6 +306,9 @@ void destroy_engine(Engine *e) {
     cudaFree(e->x); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->h);
     cudaFree(e->rope_cs); cudaFree(e->d_pos); cudaFree(e->d_next); cudaFree(e->d_history);
     cudaFree(e->attn_scratch); cudaFree(e->hidden); cudaFree(e->d_layers); cudaFree(e->step_scratch);
+    for (int r = 0; r < e->tp_size; ++r)
+        if (e->tp_connected && r != e->tp_rank && e->peers[r]) cudaIpcCloseMemHandle(e->peers[r]);
+    cudaFree(e->exchange); cudaFree(e->x_alt);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -325,12 +346,14 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
     if (!device_status_ptr()) return fail(LLMB_ERR_CUDA, "init_cache: could not allocate the device status word");
     Engine *e = new Engine();
     e->model = m;
+    e->tp_rank = m->tp_rank;
+    e->tp_size = m->tp_size;
     e->d = c.d_model;
-    e->nq = c.n_q_heads;
-    e->nkv = c.n_kv_heads;
+    e->nq = c.n_q_heads / m->tp_size;    // this rank's shares (model.cu: shard_of)
+    e->nkv = c.n_kv_heads / m->tp_size;
     e->hd = c.head_dim;
-    e->ffn = c.ffn;
-    e->vocab = c.vocab;
+    e->ffn = c.ffn / m->tp_size;
+    e->vocab = c.vocab / m->tp_size;
     e->embed_rows = m->embed_tokens->shape[0];
     e->layers = m->n_layers;
     e->max_seq = c.max_seq;
@@ -360,6 +383,12 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
     e->step_scratch_bytes = llmb_decode_step_scratch_bytes(e->nq, e->nkv, e->hd, e->step_max_splits);
     alloc(&e->step_scratch, e->step_scratch_bytes);
     alloc(reinterpret_cast<void **>(&e->d_layers), sizeof(LlmbLayer) * (size_t)e->layers);
+    if (e->tp_size > 1) {
+        e->exchange_bytes = llmb_decode_step_exchange_bytes(e->tp_size, e->d);
+        alloc(&e->exchange, e->exchange_bytes);  // plain cudaMalloc: exportable with cudaIpcGetMemHandle
+        alloc(reinterpret_cast<void **>(&e->x_alt), (size_t)e->d * 2);
+        e->peers[e->tp_rank] = e->exchange;
+    }
     if (ce == cudaSuccess) {
         std::vector<LlmbLayer> hl((size_t)e->layers);
         for (int l = 0; l < e->layers; ++l) {
@@ -382,6 +411,10 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         const int G = e->nq / e->nkv;
         e->use_step_kernel = coop && G <= 8 && e->d <= 8192 && e->ffn <= 16384 && n_q <= 16384;
+        if (e->tp_size > 1 && !e->use_step_kernel && ce == cudaSuccess) {
+            destroy_engine(e);
+            return fail(LLMB_ERR_UNSUPPORTED, "init_cache: tensor parallelism needs the whole-step kernel (cooperative launch)");
+        }
     }
     if (ce == cudaSuccess) ce = cudaMallocHost(reinterpret_cast<void **>(&e->h_next), 256);
     for (auto &ev : e->ev)
@@ -397,6 +430,9 @@ extern "C" CudaCache *llama3_init_cache(Llama3 *m, int *status_out) {
         free(cache);
         return fail(code, nullptr);
     }
+    // The buffers were cleared on the legacy stream; the engine's stream does not wait for that one,
+    // and with tensor parallelism a peer may write into the exchange block as soon as it is connected.
+    cudaDeviceSynchronize();
     cache->priv = e;
     cache->PN_X = nullptr;
     cache->Q = make_view_tensor(1, (int)n_q, e->q);
@@ -457,7 +493,41 @@ extern "C" int cache_reset(CudaCache *cache) {
 extern "C" int cache_use_step_kernel(CudaCache *cache, int enable) {
     Engine *e = eng(cache);
     if (!e) return LLMB_ERR_INVALID;
+    if (!enable && e->tp_size > 1) {
+        set_last_error("tensor parallel decode runs in the whole-step kernel only");
+        return LLMB_ERR_UNSUPPORTED;
+    }
     e->use_step_kernel = enable != 0;
+    return LLMB_OK;
+}
+
+// Tensor parallel set-up, one process per GPU: every rank exports its exchange block as a CUDA IPC
+// handle (64 bytes), the caller gathers the handles of all ranks in rank order (any transport:
+// torch.distributed, MPI, a file) and hands the table to cache_tp_connect, which maps the peers'
+// blocks into this process.
+extern "C" int cache_tp_handle(CudaCache *cache, void *handle_out) {
+    Engine *e = eng(cache);
+    if (!e || !handle_out || e->tp_size < 2) return LLMB_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    LLMB_CUDA_OK(cudaIpcGetMemHandle(&h, e->exchange));
+    memcpy(handle_out, &h, sizeof h);
+    return LLMB_OK;
+}
+
+extern "C" int cache_tp_connect(CudaCache *cache, const void *handles) {
+    Engine *e = eng(cache);
+    if (!e || !handles || e->tp_size < 2) return LLMB_ERR_INVALID;
+    if (e->tp_connected) return LLMB_OK;
+    for (int r = 0; r < e->tp_size; ++r) {
+        if (r == e->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const unsigned char *>(handles) + (size_t)r * sizeof h, sizeof h);
+        void *ptr = nullptr;
+        LLMB_CUDA_OK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        e->peers[r] = ptr;
+    }
+    e->tp_connected = true;
     return LLMB_OK;
 }
 
@@ -487,6 +557,19 @@ extern "C" int cache_read_hidden(CudaCache *cache, uint16_t *h_out) {
     if (!e || !e->hidden || !h_out) return LLMB_ERR_INVALID;
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
     LLMB_CUDA_OK(cudaMemcpy(h_out, e->hidden, (size_t)(e->layers + 1) * e->d * 2, cudaMemcpyDeviceToHost));
+    return LLMB_OK;
+}
+
+// White-box access for tests: copies one of the engine's device buffers to the host.
+// which: 0 = x, 1 = x_alt, 2 = q, 3 = attention output, 4 = h, 5 = this rank's exchange block.
+extern "C" int cache_debug_read(CudaCache *cache, int which, void *out, size_t bytes) {
+    Engine *e = eng(cache);
+    if (!e || !out) return LLMB_ERR_INVALID;
+    const void *src = which == 0 ? (void *)e->x : which == 1 ? (void *)e->x_alt : which == 2 ? (void *)e->q
+                    : which == 3 ? (void *)e->attn : which == 4 ? (void *)e->h : which == 5 ? e->exchange : nullptr;
+    if (!src) return LLMB_ERR_INVALID;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    LLMB_CUDA_OK(cudaMemcpy(out, src, bytes, cudaMemcpyDeviceToHost));
     return LLMB_OK;
 }
 

@@ -141,9 +141,13 @@ extern "C" int llama3_set_config(Llama3 *m, const Llama3Config *c) {
 
 extern "C" int llama3_set_tp(Llama3 *m, int tp_rank, int tp_size) {
     if (!m || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return LLMB_ERR_INVALID;
-    if (tp_size != 1) {
-        set_last_error("tensor parallel sharding is not built yet: tp_size must be 1");
+    if (tp_size > 8) {
+        set_last_error("llama3_set_tp: at most 8 tensor-parallel ranks (one NVSwitch domain)");
         return LLMB_ERR_UNSUPPORTED;
+    }
+    if (m->config_ready) {
+        set_last_error("llama3_set_tp: call before to_cuda / llama3_synth_weights");
+        return LLMB_ERR_INVALID;
     }
     m->tp_rank = tp_rank;
     m->tp_size = tp_size;
@@ -225,25 +229,82 @@ static int derive_config(Llama3 *m) {
     return LLMB_OK;
 }
 
+// The window of a tensor that tensor-parallel rank `rank` of `size` keeps (SURVEY 8e of the task:
+// q/k/v, gate/up and lm_head by output rows, o_proj and down_proj by input columns, the rest whole).
+struct Shard {
+    int row0, rows, col0, cols, full_cols;
+    size_t elems() const { return (size_t)rows * cols; }
+};
+
+static Shard shard_of(const Tensor *t, int layer, int slot, int rank, int size) {
+    Shard s;
+    s.full_cols = *t->ndim == 2 ? t->shape[1] : 1;
+    s.row0 = 0; s.rows = t->shape[0]; s.col0 = 0; s.cols = s.full_cols;
+    if (size == 1) return s;
+    const bool by_rows = (layer < 0 && slot == LLMB_SID_LM_HEAD) ||
+                         (layer >= 0 && (slot == LLMB_SLOT_Q || slot == LLMB_SLOT_K || slot == LLMB_SLOT_V ||
+                                         slot == LLMB_SLOT_GATE || slot == LLMB_SLOT_UP));
+    const bool by_cols = layer >= 0 && (slot == LLMB_SLOT_O || slot == LLMB_SLOT_DOWN);
+    if (by_rows) { s.rows = t->shape[0] / size; s.row0 = rank * s.rows; }
+    if (by_cols) { s.cols = s.full_cols / size; s.col0 = rank * s.cols; }
+    return s;
+}
+
+// Host-only view of the sharding plan (tests, loaders that slice at read time): the window of the
+// tensor in (layer, slot) that this model's rank keeps, as {row0, rows, col0, cols, full_cols}.
+// layer = -1 with slot LLMB_SID_EMBED / LLMB_SID_LM_HEAD / LLMB_SID_NORM names the global tensors.
+extern "C" int llama3_tensor_shard(Llama3 *m, int layer, int slot, int out[5]) {
+    if (!m || !out) return LLMB_ERR_INVALID;
+    Tensor *found = nullptr;
+    for_each_tensor(m, [&](Tensor *t, int l, int s) {
+        if (l == layer && s == slot) found = t;
+    });
+    if (!found || !found->loaded || !found->shape) return LLMB_ERR_INVALID;
+    const Shard sh = shard_of(found, layer, slot, m->tp_rank, m->tp_size);
+    out[0] = sh.row0; out[1] = sh.rows; out[2] = sh.col0; out[3] = sh.cols; out[4] = sh.full_cols;
+    return LLMB_OK;
+}
+
+static int check_tp(const Llama3 *m) {
+    const Llama3Config &c = m->config;
+    const int k = m->tp_size;
+    if (k == 1) return LLMB_OK;
+    if (c.n_q_heads % k || c.n_kv_heads % k || c.ffn % (8 * k) || c.vocab % k) {
+        set_last_error("tensor parallel size must divide the query heads, the KV heads, ffn / 8 and the vocabulary");
+        return LLMB_ERR_INVALID;
+    }
+    return LLMB_OK;
+}
+
 // Destination of each tensor on the device; allocates own buffers and the fused QKV buffer.
 static int place_tensors(Llama3 *m) {
     const Llama3Config &c = m->config;
-    auto own = [](Tensor *t) -> int {
+    const int rank = m->tp_rank, size = m->tp_size;
+    int cur_layer = -1, cur_slot = 0;
+    auto own = [&](Tensor *t) -> int {
         void *p = nullptr;
-        LLMB_CUDA_OK(cudaMalloc(&p, (size_t)(*t->mem_len) * 2));
+        LLMB_CUDA_OK(cudaMalloc(&p, shard_of(t, cur_layer, cur_slot, rank, size).elems() * 2));
         t->d_fp16_tensor = static_cast<llmb_half *>(p);
         t->device_is_view = 0;
         return LLMB_OK;
     };
     int rc;
-    if ((rc = own(m->embed_tokens)) || (rc = own(m->lm_head)) || (rc = own(m->norm))) return rc;
-    const size_t q_elems = (size_t)c.n_q_heads * c.head_dim * c.d_model;
-    const size_t kv_elems = (size_t)c.n_kv_heads * c.head_dim * c.d_model;
+    auto own_as = [&](Tensor *t, int layer, int slot) {
+        cur_layer = layer;
+        cur_slot = slot;
+        return own(t);
+    };
+    if ((rc = own_as(m->embed_tokens, -1, LLMB_SID_EMBED)) || (rc = own_as(m->lm_head, -1, LLMB_SID_LM_HEAD)) ||
+        (rc = own_as(m->norm, -1, LLMB_SID_NORM)))
+        return rc;
+    const size_t q_elems = (size_t)c.n_q_heads / size * c.head_dim * c.d_model;
+    const size_t kv_elems = (size_t)c.n_kv_heads / size * c.head_dim * c.d_model;
     for (int i = 0; i < m->n_layers; ++i) {
         Llama3Layer *l = m->layers[i];
-        if ((rc = own(l->input_layernorm)) || (rc = own(l->post_attention_layernorm)) ||
-            (rc = own(l->self_attn_o_proj)) || (rc = own(l->mlp_gate_proj)) || (rc = own(l->mlp_up_proj)) ||
-            (rc = own(l->mlp_down_proj)))
+        if ((rc = own_as(l->input_layernorm, i, LLMB_SLOT_INPUT_LAYERNORM)) ||
+            (rc = own_as(l->post_attention_layernorm, i, LLMB_SLOT_POST_LAYERNORM)) ||
+            (rc = own_as(l->self_attn_o_proj, i, LLMB_SLOT_O)) || (rc = own_as(l->mlp_gate_proj, i, LLMB_SLOT_GATE)) ||
+            (rc = own_as(l->mlp_up_proj, i, LLMB_SLOT_UP)) || (rc = own_as(l->mlp_down_proj, i, LLMB_SLOT_DOWN)))
             return rc;
         void *qkv = nullptr;
         LLMB_CUDA_OK(cudaMalloc(&qkv, (q_elems + 2 * kv_elems) * 2));
@@ -258,31 +319,43 @@ static int place_tensors(Llama3 *m) {
     return LLMB_OK;
 }
 
+// After the upload a Tensor describes what is on the device: the shard's shape.
+static void set_local_shape(Tensor *t, const Shard &s) {
+    t->shape[0] = s.rows;
+    if (*t->ndim == 2) t->shape[1] = s.cols;
+    *t->mem_len = (int)s.elems();
+}
+
 extern "C" int llama3_to_cuda(Llama3 *m) {
     if (!m) return LLMB_ERR_INVALID;
     int rc = derive_config(m);
     if (rc) return rc;
+    if ((rc = check_tp(m))) return rc;
     if ((rc = place_tensors(m))) return rc;
+    const int rank = m->tp_rank, size = m->tp_size;
     size_t max_elems = 0;
-    for_each_tensor(m, [&](Tensor *t, int, int) {
-        if ((size_t)*t->mem_len > max_elems) max_elems = (size_t)*t->mem_len;
+    for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
+        const size_t n = shard_of(t, layer, slot, rank, size).elems();
+        if (n > max_elems) max_elems = n;
     });
     void *staging = nullptr;
     LLMB_CUDA_OK(cudaMalloc(&staging, max_elems * 2));
     int status = LLMB_OK;
-    for_each_tensor(m, [&](Tensor *t, int, int) {
+    for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
         if (status) return;
         if (!t->bf16_tensor) {
             set_last_error("to_cuda: tensor payload missing on the host");
             status = LLMB_ERR_INVALID;
             return;
         }
-        const size_t n = (size_t)*t->mem_len;
-        cudaError_t e;
-        if (t->file_dtype == 1) {  // F16 file: pass through
-            e = cudaMemcpy(t->d_fp16_tensor, t->bf16_tensor, n * 2, cudaMemcpyHostToDevice);
-        } else {
-            e = cudaMemcpy(staging, t->bf16_tensor, n * 2, cudaMemcpyHostToDevice);
+        const Shard sh = shard_of(t, layer, slot, rank, size);
+        const size_t n = sh.elems();
+        // this rank's window of the host tensor: rows [row0, row0 + rows), columns [col0, col0 + cols)
+        const uint16_t *src = t->bf16_tensor + (size_t)sh.row0 * sh.full_cols + sh.col0;
+        void *dst = (t->file_dtype == 1) ? static_cast<void *>(t->d_fp16_tensor) : staging;
+        cudaError_t e = cudaMemcpy2D(dst, (size_t)sh.cols * 2, src, (size_t)sh.full_cols * 2, (size_t)sh.cols * 2,
+                                     (size_t)sh.rows, cudaMemcpyHostToDevice);
+        if (t->file_dtype != 1) {  // BF16 file: convert on the device (F16 files pass through)
             if (e == cudaSuccess) {
                 int r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(staging),
                                           reinterpret_cast<uint16_t *>(t->d_fp16_tensor), n, nullptr);
@@ -293,6 +366,7 @@ extern "C" int llama3_to_cuda(Llama3 *m) {
         if (e != cudaSuccess && !status) status = cuda_fail(e, __FILE__, __LINE__);
         free(t->bf16_tensor);  // llama3.cu:211
         t->bf16_tensor = nullptr;
+        set_local_shape(t, sh);
     });
     cudaFree(staging);
     return status;
@@ -332,31 +406,39 @@ extern "C" int llama3_synth_weights(Llama3 *m, const Llama3Config *cfg, uint64_t
     }
     if (rc) return LLMB_ERR_INVALID;
     if ((rc = derive_config(m))) return rc;
+    if ((rc = check_tp(m))) return rc;
     if ((rc = place_tensors(m))) return rc;
+    const int rank = m->tp_rank, size = m->tp_size;
     size_t max_elems = 0;
-    for_each_tensor(m, [&](Tensor *t, int, int) {
-        if ((size_t)*t->mem_len > max_elems) max_elems = (size_t)*t->mem_len;
+    for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
+        const size_t n = shard_of(t, layer, slot, rank, size).elems();
+        if (n > max_elems) max_elems = n;
     });
     void *staging = nullptr;
     if (bf16) LLMB_CUDA_OK(cudaMalloc(&staging, max_elems * 2));
     int status = LLMB_OK;
     for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
         if (status) return;
-        const uint64_t n = (uint64_t)*t->mem_len;
+        const Shard sh = shard_of(t, layer, slot, rank, size);
+        const uint64_t n = sh.elems();
         const bool is_norm = (layer < 0 && slot == LLMB_SID_NORM) ||
                              (layer >= 0 && (slot == LLMB_SLOT_INPUT_LAYERNORM || slot == LLMB_SLOT_POST_LAYERNORM));
         const uint64_t sid = layer < 0 ? (uint64_t)slot : LLMB_LAYER_SID(layer, slot);
         uint16_t *dst = reinterpret_cast<uint16_t *>(t->d_fp16_tensor);
+        // element (r, c) of the shard is element (row0 + r) * full_cols + col0 + c of the whole tensor
+        const uint64_t first = (uint64_t)sh.row0 * sh.full_cols + sh.col0;
         int r;
         if (is_norm) {
             r = llmb_fill_u16(dst, 0x3C00, n, nullptr);  // gain 1.0
         } else if (bf16) {
-            r = llmb_synth_bf16(static_cast<uint16_t *>(staging), seed, sid, 0.02f, 0, n, nullptr);
+            r = llmb_synth_2d(static_cast<uint16_t *>(staging), seed, sid, 0.02f, 1, first, sh.full_cols, sh.rows, sh.cols,
+                              nullptr);
             if (!r) r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(staging), dst, n, nullptr);
         } else {
-            r = llmb_synth_fp16(dst, seed, sid, 0.02f, 0, n, nullptr);
+            r = llmb_synth_2d(dst, seed, sid, 0.02f, 0, first, sh.full_cols, sh.rows, sh.cols, nullptr);
         }
         if (r) status = r;
+        set_local_shape(t, sh);
     });
     cudaError_t e = cudaDeviceSynchronize();
     if (staging) cudaFree(staging);

@@ -121,7 +121,9 @@ def test_to_cuda_rejects_incomplete_model(pkg, model):
     assert b"never loaded" in pkg.lib.llmb_last_error()
 
 
-def test_tp_is_refused_until_built(pkg, model):
+def test_tp_arguments(pkg, model):
     assert pkg.lib.llama3_set_tp(model, 0, 1) == 0
-    assert pkg.lib.llama3_set_tp(model, 1, 2) == pkg.ERR_UNSUPPORTED
+    assert pkg.lib.llama3_set_tp(model, 1, 2) == 0
+    assert pkg.lib.llama3_set_tp(model, 7, 8) == 0
     assert pkg.lib.llama3_set_tp(model, 2, 2) == pkg.ERR_INVALID
+    assert pkg.lib.llama3_set_tp(model, 0, 16) == pkg.ERR_UNSUPPORTED
