@@ -179,6 +179,11 @@ int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int *out_tokens
 /* Test aid: copies an internal device buffer to the host (0 = residual row x, 1 = second residual
  * buffer, 2 = q, 3 = attention output, 4 = SwiGLU output h, 5 = this rank's exchange block). */
 int cache_debug_read(CudaCache *cache, int which, void *out, size_t bytes);
+/* Profiling aid: makes the step kernel record per-phase timestamps of every CTA; read with
+ * cache_debug_read(cache, 6, ...) as [SM count][5 * n_layers + 2][8] uint64 nanoseconds
+ * (consumers: entered, dependency met, input ready, done; finisher: started, first stage, last
+ * stage, fenced). */
+int cache_debug_trace(CudaCache *cache, int enable);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

@@ -220,9 +220,10 @@ typedef struct {
     int tp_rank, tp_size, vocab_offset;
     uint16_t *x_alt;        /* [d_model] second residual buffer */
     void *peers[8];
-    uint64_t *trace;        /* optional profiling aid, device [SM count][5 * n_layers + 2][4] nanosecond
-                               stamps, one row per CTA; per phase: entered, dependency met, input ready,
-                               done.  NULL in production. */
+    uint64_t *trace;        /* optional profiling aid, device [SM count][5 * n_layers + 2][8] nanosecond
+                               stamps, one row per CTA; per phase: consumers entered, dependency met, input
+                               ready, done; finisher started, first stage, last stage, fenced.  NULL in
+                               production. */
 } LlmbDecodeStepArgs;
 
 size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits);

@@ -30,7 +30,7 @@ HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
-    "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read",
+    "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
     "cache_kernel_launches",
 ]
 
@@ -153,6 +153,7 @@ def _declare(l):
                                    C.POINTER(C.c_float)]
     l.inference_continue.argtypes = [M, K, i32, C.POINTER(C.c_int), C.POINTER(C.c_float)]
     l.cache_debug_read.argtypes = [K, i32, vp, sz]
+    l.cache_debug_trace.argtypes = [K, i32]
     l.cache_kernel_launches.argtypes = [K]
     l.cache_kernel_launches.restype = C.c_longlong
 

@@ -68,7 +68,7 @@ struct DsParams {
     float *amax_val;          // [gridDim]
     int *amax_idx;
     int *status;
-    unsigned long long *trace;  // optional: [gridDim][phases][4] globaltimer stamps
+    unsigned long long *trace;  // optional: [gridDim][phases][8] globaltimer stamps
     double eps;
     float rope_theta;
     int n_layers, d, nq, nkv, hd, ffn, vocab, embed_rows, max_pos;
@@ -83,7 +83,11 @@ struct DsParams {
 //   [0, 64)      flags[r]  u64: highest synchronisation number rank r has announced
 //   [128, 136)   this rank's own count of synchronisations so far (local, persists across launches)
 //   [256, 512)   best[r]   (float value, int index): rank r's best logit of this step
-//   [512, ...)   recv[2][tp_size][d_model] FP32: partial projection sums, double-buffered
+//   [136, 144)   this rank's count of all-reduces so far (the tag base; local, persists)
+//   [512, ...)   recv[2][tp_size][d_model] of (FP32 partial sum, 32-bit tag): double-buffered.  A value
+//                and its tag travel in one 8-byte store, and a reader spins until the tag is the number
+//                of the all-reduce it is performing, so no fence, flag or barrier stands between a
+//                projection and the all-reduced row (the low-latency protocol of collective libraries).
 constexpr size_t kTpFlagsOff = 0, kTpBestOff = 256, kTpRecvOff = 512;
 
 enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
@@ -285,7 +289,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     // End of a phase for this CTA: all its global writes are ordered before the arrival.
     // the cross-GPU synchronisation number lives in this rank's exchange block (never reset locally)
     unsigned long long *tp_state = p.tp_size > 1 ? reinterpret_cast<unsigned long long *>(p.peer[p.tp_rank] + 128) : nullptr;
-    const unsigned long long tp_base = tp_state ? *tp_state : 0ULL;
+    const unsigned long long tp_base = tp_state ? tp_state[0] : 0ULL;
+    const unsigned int tag_base = tp_state ? (unsigned int)tp_state[1] : 0u;  // all-reduces done before this launch
     unsigned long long n_tp = 0;   // cross-GPU synchronisations passed in this launch
     auto grid_arrive = [&]() {
         named_bar_sync(3, kDsThreads);
@@ -311,47 +316,12 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         named_bar_sync(3, kDsThreads);
         if (sh.abort_flag) ok = false;
     };
-    // All ranks have finished the phase: the local wait, then CTA 0 announces it to the peers and
-    // every CTA waits until each peer has announced the same synchronisation number.
-    auto grid_wait_all_ranks = [&]() {
-        ++n_bar;
-        ++n_tp;
-        if (tid == 0 && ok) {
-            const unsigned long long target = bar_base + n_bar * (unsigned long long)gridDim.x;
-            const unsigned long long seq = tp_base + n_tp;
-            uint32_t polls = 0;
-            bool fine = true;
-            while (ld_acquire_u64(p.bar) < target) {
-                if (++polls > kPollLimit) { fine = false; break; }
-            }
-            if (fine && blockIdx.x == 0) {
-                __threadfence_system();
-                for (int r = 0; r < p.tp_size; ++r)
-                    if (r != p.tp_rank)
-                        *reinterpret_cast<volatile unsigned long long *>(p.peer[r] + kTpFlagsOff + 8 * p.tp_rank) = seq;
-            }
-            for (int r = 0; r < p.tp_size && fine; ++r) {
-                if (r == p.tp_rank) continue;
-                const unsigned long long *f = reinterpret_cast<const unsigned long long *>(p.peer[p.tp_rank] + kTpFlagsOff + 8 * r);
-                unsigned long long v;
-                polls = 0;
-                do {
-                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
-                    if (++polls > kPollLimit) { fine = false; break; }
-                } while (v < seq);
-            }
-            if (!fine) {
-                atomicExch(p.status, 205);
-                sh.abort_flag = 1;
-            }
-        }
-        named_bar_sync(3, kDsThreads);
-        if (sh.abort_flag) ok = false;
-    };
-    // the wait that follows projection `ph`: across ranks where its output is an all-reduced sum
+    // the wait that follows projection `ph`
     auto wait_after = [&](int prev_ph) {
         const int kind = (prev_ph < 4 * p.n_layers) ? (prev_ph & 3) : PH_LM;
-        if (p.tp_size > 1 && (kind == PH_O || kind == PH_DOWN)) grid_wait_all_ranks();
+        // tensor parallel: the partial sums of o_proj / down_proj carry their own tags, so the next
+        // phase needs no grid-wide wait at all; the arrival is still counted
+        if (p.tp_size > 1 && (kind == PH_O || kind == PH_DOWN)) ++n_bar;
         else grid_wait();
     };
 
@@ -370,9 +340,17 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         float best_val = -INFINITY;
         int best_idx = 0x7fffffff;
         uint32_t it = 0;
+        // profiling aid: the finisher's own stamps go to slots 4..6 of the phase's trace row
+        auto fstamp = [&](int ph, int which) {
+            if (p.trace && lane == 0) {
+                const int tph = ph + (ph + 3) / 4;  // attention phases are interleaved after each QKV
+                p.trace[((size_t)blockIdx.x * (5 * p.n_layers + 2) + tph) * 8 + which] = globaltimer_ns();
+            }
+        };
         for (int ph = 0; ph < n_gemv; ++ph) {
             const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
             if (ph > 0) wait_after(ph - 1);
+            fstamp(ph, 4);
             int gb, ge;
             cta_range((g.n + g.R - 1) / g.R, gb, ge);
             const unsigned mask = (1u << g.nr) - 1u;
@@ -395,6 +373,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     got = mbar_wait_warp(&sh.done_bar[s], (it / kDsSlots) & 1, p.status, 204, lane);
                     if (!got) sh.abort_flag = 1;
                 }
+                if (rg == gb) fstamp(ph, 5);
                 if (got && lane < g.nr) {
                     const float *rp = sh.red[s][lane];
                     const float sum = ((rp[0] + rp[1]) + (rp[2] + rp[3])) + ((rp[4] + rp[5]) + (rp[6] + rp[7]));
@@ -417,8 +396,12 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     } else if (g.scatter >= 0) {
                         // tensor parallel: this rank's partial sum goes to every rank's receive buffer
                         if (lane < rows) {
-                            const size_t off = kTpRecvOff + (((size_t)(g.scatter & 1) * p.tp_size + p.tp_rank) * p.d + row0 + lane) * 4;
-                            for (int r = 0; r < p.tp_size; ++r) *reinterpret_cast<float *>(p.peer[r] + off) = sum;
+                            const size_t off = kTpRecvOff + (((size_t)(g.scatter & 1) * p.tp_size + p.tp_rank) * p.d + row0 + lane) * 8;
+                            const unsigned int tag = tag_base + (unsigned int)g.scatter + 1u;
+                            for (int r = 0; r < p.tp_size; ++r)
+                                asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.peer[r] + off),
+                                             "r"(__float_as_uint(sum)), "r"(tag)
+                                             : "memory");
                         }
                     } else if (g.kind == PH_O || g.kind == PH_DOWN) {
                         if (lane < rows) {
@@ -452,7 +435,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             }
             // Stores into the peers' memory are posted over NVLink: the warp that issued them waits for
             // them itself, a fence by another thread after a CTA barrier does not cover them.
-            if (g.scatter >= 0) __threadfence_system();
+            fstamp(ph, 6);
             if (g.kind == PH_LM && lane == 0) {  // this CTA's best logit travels with the phase's arrival
                 p.amax_val[blockIdx.x] = best_val;
                 p.amax_idx[blockIdx.x] = best_idx;
@@ -484,7 +467,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     // profiling aid: thread 0 of every CTA stamps the global timer four times per phase
     const int trace_row = (p.trace && tid == 0) ? (int)blockIdx.x : -1;
     auto stamp = [&](int phase, int which) {
-        if (trace_row >= 0) p.trace[((size_t)trace_row * (5 * p.n_layers + 2) + phase) * 4 + which] = globaltimer_ns();
+        if (trace_row >= 0) p.trace[((size_t)trace_row * (5 * p.n_layers + 2) + phase) * 8 + which] = globaltimer_ns();
     };
     int tphase = 0;
     uint32_t it = 0;
@@ -520,8 +503,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             // row, x = half(float(half(sum over ranks of partials)) + float(x_old)): the reference's
             // rounding points (inference.cu:445, :385-387) with the sum taken in rank order.  Every CTA
             // forms the whole row for itself; the chunk's owner CTA also stores it for later residual adds.
-            const float *recv = reinterpret_cast<const float *>(p.peer[p.tp_rank] + kTpRecvOff) +
-                                (size_t)(g.reduce & 1) * p.tp_size * p.d;
+            const unsigned char *recv = p.peer[p.tp_rank] + kTpRecvOff + (size_t)(g.reduce & 1) * p.tp_size * p.d * 8;
+            const unsigned int tag = tag_base + (unsigned int)g.reduce + 1u;
 #pragma unroll
             for (int j = 0; j < kDsJ / 2; ++j) {
                 xh[j] = make_uint4(0, 0, 0, 0);
@@ -531,10 +514,32 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
 #pragma unroll
                     for (int e = 0; e < 8; ++e) acc8[e] = 0.0f;
                     for (int r = 0; r < p.tp_size; ++r) {
-                        const float4 a = __ldcg(reinterpret_cast<const float4 *>(recv + (size_t)r * p.d + c * 8));
-                        const float4 b = __ldcg(reinterpret_cast<const float4 *>(recv + (size_t)r * p.d + c * 8 + 4));
-                        acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
-                        acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+                        // eight (value, tag) pairs = four 16-byte loads; spin until every tag is this all-reduce's
+                        const unsigned char *src = recv + ((size_t)r * p.d + (size_t)c * 8) * 8;
+                        uint4 q[4];
+                        uint32_t spins = 0;
+                        for (;;) {
+                            bool all = true;
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                             : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
+                                             : "l"(src + 16 * u)
+                                             : "memory");
+                                all = all && q[u].y == tag && q[u].w == tag;
+                            }
+                            if (all || !ok) break;
+                            if (++spins > kPollLimit) {
+                                atomicExch(p.status, 205);
+                                sh.abort_flag = 1;
+                                break;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            acc8[2 * u] += __uint_as_float(q[u].x);
+                            acc8[2 * u + 1] += __uint_as_float(q[u].z);
+                        }
                     }
                     const uint4 xo = __ldcg(reinterpret_cast<const uint4 *>(g.x_old) + c);
                     float xf[8];
@@ -877,7 +882,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             }
             *p.pos = np;
             p.bar[1] = bar_base + n_bar * (unsigned long long)gridDim.x;
-            if (tp_state) *tp_state = tp_base + n_tp;
+            if (tp_state) {
+                tp_state[0] = tp_base + n_tp;
+                tp_state[1] = (unsigned long long)(tag_base + 2u * (unsigned int)p.n_layers);
+            }
         }
     }
 }
@@ -890,7 +898,7 @@ static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 extern "C" size_t llmb_decode_step_exchange_bytes(int tp_size, int d_model) {
     if (tp_size < 1 || d_model <= 0) return 0;
-    return kTpRecvOff + (size_t)2 * tp_size * d_model * sizeof(float);
+    return kTpRecvOff + (size_t)2 * tp_size * d_model * 8;
 }
 
 extern "C" size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {

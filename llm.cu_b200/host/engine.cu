@@ -65,6 +65,8 @@ struct Engine {
     size_t exchange_bytes = 0;
     void *peers[8] = {};                // every rank's block as mapped on this device
     bool tp_connected = false;
+    unsigned long long *trace = nullptr;  // optional per-phase timestamps of the step kernel
+    size_t trace_bytes = 0;
     int *h_next = nullptr;  // pinned
     __half *hidden = nullptr;
     bool use_graph = true, use_pdl = true, copy_logits = true, hidden_dump = false;
@@ -236,6 +238,7 @@ int launch_step_kernel(Engine *e, bool with_logits, int len) {
     a.n_splits = (len + split_len - 1) / split_len;
     a.with_logits = with_logits ? 1 : 0;
     a.hidden = e->hidden_dump ? reinterpret_cast<uint16_t *>(e->hidden) : nullptr;
+    a.trace = reinterpret_cast<uint64_t *>(e->trace);
     if (e->tp_size > 1) {
         if (!e->tp_connected) {
             set_last_error("tensor parallel cache: call cache_tp_connect() on every rank first");
@@ -308,7 +311,7 @@ void destroy_engine(Engine *e) {
     cudaFree(e->attn_scratch); cudaFree(e->hidden); cudaFree(e->d_layers); cudaFree(e->step_scratch);
     for (int r = 0; r < e->tp_size; ++r)
         if (e->tp_connected && r != e->tp_rank && e->peers[r]) cudaIpcCloseMemHandle(e->peers[r]);
-    cudaFree(e->exchange); cudaFree(e->x_alt);
+    cudaFree(e->exchange); cudaFree(e->x_alt); cudaFree(e->trace);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -560,13 +563,33 @@ extern "C" int cache_read_hidden(CudaCache *cache, uint16_t *h_out) {
     return LLMB_OK;
 }
 
+// Profiling aid: per-phase timestamps of every CTA of the step kernel (last step wins); read them
+// back with cache_debug_read(cache, 6, ...): [SM count][5 * n_layers + 2][8] uint64 nanoseconds.
+extern "C" int cache_debug_trace(CudaCache *cache, int enable) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    if (enable && !e->trace) {
+        e->trace_bytes = (size_t)e->sm_count * (5 * e->layers + 2) * 8 * sizeof(unsigned long long);
+        LLMB_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&e->trace), e->trace_bytes));
+        LLMB_CUDA_OK(cudaMemset(e->trace, 0, e->trace_bytes));
+        LLMB_CUDA_OK(cudaDeviceSynchronize());
+    } else if (!enable && e->trace) {
+        LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+        cudaFree(e->trace);
+        e->trace = nullptr;
+    }
+    return LLMB_OK;
+}
+
 // White-box access for tests: copies one of the engine's device buffers to the host.
-// which: 0 = x, 1 = x_alt, 2 = q, 3 = attention output, 4 = h, 5 = this rank's exchange block.
+// which: 0 = x, 1 = x_alt, 2 = q, 3 = attention output, 4 = h, 5 = this rank's exchange block,
+// 6 = the step kernel's trace.
 extern "C" int cache_debug_read(CudaCache *cache, int which, void *out, size_t bytes) {
     Engine *e = eng(cache);
     if (!e || !out) return LLMB_ERR_INVALID;
     const void *src = which == 0 ? (void *)e->x : which == 1 ? (void *)e->x_alt : which == 2 ? (void *)e->q
-                    : which == 3 ? (void *)e->attn : which == 4 ? (void *)e->h : which == 5 ? e->exchange : nullptr;
+                    : which == 3 ? (void *)e->attn : which == 4 ? (void *)e->h : which == 5 ? e->exchange
+                    : which == 6 ? (void *)e->trace : nullptr;
     if (!src) return LLMB_ERR_INVALID;
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
     LLMB_CUDA_OK(cudaMemcpy(out, src, bytes, cudaMemcpyDeviceToHost));
