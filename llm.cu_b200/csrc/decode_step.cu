@@ -49,6 +49,7 @@ constexpr uint32_t kDsSlotBytes = 32 * 1024;
 constexpr int kDsJ = 8;                           // 16-byte chunks of x per thread: k <= 16384
 constexpr int kDsTile = 32;                       // cache rows per attention tile
 constexpr uint32_t kPollLimit = 1u << 22;
+constexpr uint32_t kTagPollLimit = 1u << 18;  // tagged peer data: about half a second
 
 struct DsLayer {
     const __half *wqkv, *wo, *wgate, *wup, *wdown, *g_in, *g_post;
@@ -284,7 +285,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     const int n_q = p.nq * p.hd, n_kv = p.nkv * p.hd;
     const unsigned long long bar_base = p.bar[1];
     unsigned long long n_bar = 0;  // grid-wide waits passed in this launch
-    bool ok = true;                // only changes right after a barrier of all 17 warps
+    // A wait that gave up in an earlier launch leaves the status word set: until the host has read
+    // and cleared it (llmb_device_status), every later launch skips all waits and just runs through,
+    // so a lost peer or a wedged ring costs one bounded wait, not one per step.
+    bool ok = *reinterpret_cast<volatile int *>(p.status) == 0;  // later only changes right after a barrier of all 17 warps
 
     // End of a phase for this CTA: all its global writes are ordered before the arrival.
     // the cross-GPU synchronisation number lives in this rank's exchange block (never reset locally)
@@ -529,7 +533,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                                 all = all && q[u].y == tag && q[u].w == tag;
                             }
                             if (all || !ok) break;
-                            if (++spins > kPollLimit) {
+                            if (++spins > kTagPollLimit) {
                                 atomicExch(p.status, 205);
                                 sh.abort_flag = 1;
                                 break;
@@ -815,6 +819,33 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             grid_arrive();
             stamp(tphase, 3);
             ++tphase;
+        }
+    }
+
+    // Tensor parallel step without logits (prompt rows): nobody consumes the last all-reduce, so a fast
+    // rank could start the next step and overwrite receive buffer 0 while a slow rank still reads it.
+    // Waiting here for every rank's last partial sums keeps the ranks within one all-reduce of each
+    // other, which is what the double buffering relies on.
+    if (p.tp_size > 1 && !p.with_logits) {
+        const int last = 2 * p.n_layers - 1;
+        const unsigned char *recv = p.peer[p.tp_rank] + kTpRecvOff + (size_t)(last & 1) * p.tp_size * p.d * 8;
+        const unsigned int tag = tag_base + (unsigned int)last + 1u;
+        for (int i = tid; i < p.tp_size * p.d / 2 && ok; i += kDsConsumers) {  // two (value, tag) pairs per load
+            uint32_t spins = 0;
+            for (;;) {
+                uint4 q;
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                             : "l"(recv + (size_t)i * 16)
+                             : "memory");
+                if (q.y == tag && q.w == tag) break;
+                if (++spins > kTagPollLimit) {
+                    atomicExch(p.status, 207);
+                    sh.abort_flag = 1;
+                    break;
+                }
+            }
+            if (sh.abort_flag) break;
         }
     }
 

@@ -303,6 +303,24 @@ int feed_tokens(Engine *e, const int *ids, int from, int to) {
     return LLMB_OK;
 }
 
+// After a synchronisation point: has any bounded device-side wait given up?  The status word stays
+// set (the kernels then skip their waits) until the caller reads it with llmb_device_status().
+int check_device_status(Engine *e) {
+    int st = 0;
+    int *p = device_status_ptr();
+    if (!p) return LLMB_ERR_CUDA;
+    LLMB_CUDA_OK(cudaMemcpyAsync(&st, p, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if (st != 0) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "a bounded device-side wait gave up (status %d)%s", st,
+                 st >= 205 && st <= 207 ? ": a tensor-parallel peer did not deliver its partial sums in time" : "");
+        set_last_error(msg);
+        return LLMB_ERR_TIMEOUT;
+    }
+    return LLMB_OK;
+}
+
 void destroy_engine(Engine *e) {
     if (!e) return;
     for (auto &kv : e->graphs) cudaGraphExecDestroy(kv.second);
@@ -654,6 +672,7 @@ extern "C" int inference(Llama3 *m, Tensor *X, int *d_tokens, int *h_tokens, Cud
     cudaMemcpyAsync(e->h_next, e->d_next, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
     cudaError_t ce = cudaStreamSynchronize(e->stream);
     if (ce != cudaSuccess) return -cuda_fail(ce, __FILE__, __LINE__);
+    if ((rc = check_device_status(e))) return -rc;
     e->consumed.assign(ids, ids + count);
     e->greedy_state = true;  // the argmax kernel appended the sampled token to the device history
     return e->h_next[0];
@@ -678,6 +697,7 @@ extern "C" int inference_greedy(Llama3 *m, CudaCache *cache, const int *prompt, 
     LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + n_prompt, sizeof(int) * (size_t)n_new,
                                  cudaMemcpyDeviceToHost, e->stream));
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if ((rc = check_device_status(e))) return rc;
     if (prefill_ms) LLMB_CUDA_OK(cudaEventElapsedTime(prefill_ms, e->ev[0], e->ev[1]));
     if (decode_ms) LLMB_CUDA_OK(cudaEventElapsedTime(decode_ms, e->ev[1], e->ev[2]));
     // the cache now holds prompt + all but the last generated token
@@ -710,6 +730,7 @@ extern "C" int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int 
     LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + P + 1, sizeof(int) * (size_t)n_steps,
                                  cudaMemcpyDeviceToHost, e->stream));
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if ((rc = check_device_status(e))) return rc;
     if (ms) LLMB_CUDA_OK(cudaEventElapsedTime(ms, e->ev[0], e->ev[1]));
     e->consumed.insert(e->consumed.end(), fed.begin(), fed.end());
     return LLMB_OK;

@@ -60,6 +60,13 @@ def _rank_main(rank, world, port, cfg_name, n_prompt, n_steps, result_path):
                 top2 = np.sort(oracle.f16(want))[-2:]
                 ok &= bool(top2[1] - top2[0] <= 2 * diff + 1e-3)
             ok &= nxt == int(oracle.lib().oracle_argmax_fp16(got.ctypes.data, len(got)))
+    # a long prompt fed without logits: the ranks drift apart here if anything lets them
+    long_prompt = oracle.synth_tokens(7, 150, vocab_ids).tolist()
+    cache.reset()
+    dist.barrier()
+    cache.greedy(long_prompt, 3)
+    cache.reset()
+    dist.barrier()
     toks, _, _ = cache.greedy(tokens[:n_prompt].tolist(), 6)
     st = __import__("ctypes").c_int(0)
     pkg.lib.llmb_device_status(__import__("ctypes").byref(st))
