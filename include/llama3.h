@@ -184,6 +184,14 @@ int cache_debug_read(CudaCache *cache, int which, void *out, size_t bytes);
  * (consumers: entered, dependency met, input ready, done; finisher: started, first stage, last
  * stage, fenced). */
 int cache_debug_trace(CudaCache *cache, int enable);
+/* Prompt phase.  By default a run of >= 16 new prompt tokens goes through the block path: all but
+ * the last token as blocks of up to 1024 rows (tensor-core projections, block attention), the last
+ * one through the decode step for its logits.  enable = 0 feeds every prompt token through the
+ * decode step instead; min_rows > 0 changes the threshold.  The block path needs the whole model
+ * on this GPU (tp_size 1) and projection widths that are multiples of 128; otherwise the decode
+ * step is used.  The reference runs its layer loop over all rows on every call
+ * (inference.cu:157-186). */
+int cache_set_prefill(CudaCache *cache, int enable, int min_rows);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

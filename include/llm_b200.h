@@ -168,6 +168,54 @@ int llmb_argmax_f16(const uint16_t *d_logits, int n, int32_t *d_token_out, int32
 int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------ */
+/* Prompt phase: M rows at once.                                                          */
+/*                                                                                        */
+/* llmb_gemm_f16: C[m][n] = A[m][k] . B[n][k]^T on the tensor cores (tcgen05.mma, FP32      */
+/* accumulators in tensor memory, operands staged by TMA).  Replaces                        */
+/* kernel_standard_tiled_gemm (inference.cu:393-449) and, with LLMB_EPI_SWIGLU,             */
+/* kernel_standard_tiled_gemm_ffn_swiglu (inference.cu:455-519) for m > 1 rows.  Epilogues, */
+/* with the reference's FP16 rounding points:                                               */
+/*   LLMB_EPI_STORE     c = half(acc)                                                        */
+/*   LLMB_EPI_RESIDUAL  c = half(float(half(acc)) + float(c))          (inference.cu:377-390) */
+/*   LLMB_EPI_ROPE_KV   n = n_q + 2 n_kv: RoPE on q and k with rope_cs[row], q -> c [m][n_q], */
+/*                      k, v -> cache row pos0 + row                     (inference.cu:640-695) */
+/*   LLMB_EPI_SWIGLU    c = half(SiLU(A.b^T) * (A.b2^T)), accumulators not rounded  (:515)     */
+/* n must be a multiple of 128, k of 64; a, b, c 16-byte aligned; m is free (rows past m are   */
+/* zero-filled on load and never stored).                                                     */
+/* ------------------------------------------------------------------------------------ */
+typedef struct {
+    const uint16_t *a;     /* [m][k] FP16 activations */
+    const uint16_t *b;     /* [n][k] FP16 weights */
+    const uint16_t *b2;    /* SWIGLU: the up projection [n][k] */
+    uint16_t *c;           /* [m][n]; ROPE_KV: [m][n_q] */
+    int m, n, k;
+    int epilogue;
+    int n_q, n_kv, head_dim;
+    const float *rope_cs;  /* [m][head_dim/2][2] from llmb_embed_rope */
+    uint16_t *k_cache;     /* [max_pos][n_kv] of this layer */
+    uint16_t *v_cache;
+    int pos0;              /* cache row of A's row 0 */
+    int max_pos;
+} LlmbGemmArgs;
+
+int llmb_gemm_f16(const LlmbGemmArgs *args, llmb_stream_t stream);
+
+/* RMSNorm of m rows of d FP16 values: y = half(x * gamma / rms(x)), the reduction order and  */
+/* rounding of kernel_compute_rms_norm / kernel_compute_norm_tensor (inference.cu:272-375).    */
+int llmb_rmsnorm_rows(const uint16_t *d_x, const uint16_t *d_gamma, uint16_t *d_y, int m, int d, double eps,
+                      llmb_stream_t stream);
+
+/* Causal attention of m new rows (positions pos0 .. pos0 + m - 1, whose K/V rows are already   */
+/* in the cache) over cache rows 0 .. pos0 + row.  Replaces compute_attention                    */
+/* (inference.cu:698-947) for a block of rows; same arithmetic as llmb_attn_decode.              */
+/*   q, out : [m][n_q_heads * head_dim] FP16;  head_dim 64 or 128                                */
+int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, int m, int pos0,
+                      int n_q_heads, int n_kv_heads, int head_dim, uint16_t *d_out, llmb_stream_t stream);
+
+/* d_out[i] = first + i: the positions of a block of prompt rows for llmb_embed_rope. */
+int llmb_iota_i32(int32_t *d_out, int first, int n, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
 /* One whole decode step as a single persistent kernel: every phase of the reference's     */
 /* inference() loop body (inference.cu:149-193) for one new row -- embedding row, per layer */
 /* RMSNorm + QKV + RoPE + cache append, attention over the cache, o_proj + residual,        */

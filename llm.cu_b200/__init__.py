@@ -24,14 +24,15 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
+    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
+    "llmb_rmsnorm_rows", "llmb_attn_prefill", "llmb_iota_i32", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
     "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
-    "cache_kernel_launches",
+    "cache_kernel_launches", "cache_set_prefill",
 ]
 
 
@@ -93,6 +94,15 @@ class GemvArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("b2", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int), ("n", C.c_int),
+        ("k", C.c_int), ("epilogue", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
+        ("rope_cs", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("pos0", C.c_int),
+        ("max_pos", C.c_int),
+    ]
+
+
 def _declare(l):
     vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
     l.llmb_last_error.restype = C.c_char_p
@@ -111,6 +121,10 @@ def _declare(l):
     l.llmb_attn_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]
     l.llmb_argmax_f16.argtypes = [vp, i32, vp, vp, vp, i32, i32, vp]
     l.llmb_advance_pos.argtypes = [vp, i32, vp]
+    l.llmb_gemm_f16.argtypes = [C.POINTER(GemmArgs), vp]
+    l.llmb_rmsnorm_rows.argtypes = [vp, vp, vp, i32, i32, C.c_double, vp]
+    l.llmb_attn_prefill.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
+    l.llmb_iota_i32.argtypes = [vp, i32, i32, vp]
     M, K = C.POINTER(Llama3Struct), C.POINTER(CudaCacheStruct)
     l.init_llama3.argtypes = [i32]
     l.init_llama3.restype = M
@@ -155,6 +169,7 @@ def _declare(l):
     l.cache_debug_read.argtypes = [K, i32, vp, sz]
     l.cache_debug_trace.argtypes = [K, i32]
     l.cache_kernel_launches.argtypes = [K]
+    l.cache_set_prefill.argtypes = [K, i32, i32]
     l.cache_kernel_launches.restype = C.c_longlong
 
 
@@ -175,5 +190,5 @@ def check(code, where):
 from .configs import CONFIGS, ModelConfig  # noqa: E402
 from .engine import Cache, Model  # noqa: E402
 
-__all__ = ["lib", "check", "LlmbError", "Llama3Config", "GemvArgs", "Model", "Cache", "CONFIGS", "ModelConfig",
+__all__ = ["lib", "check", "LlmbError", "Llama3Config", "GemvArgs", "GemmArgs", "Model", "Cache", "CONFIGS", "ModelConfig",
            "KERNEL_SYMBOLS", "HOST_SYMBOLS", "LIB_PATH"]

@@ -17,6 +17,8 @@ SOURCES = [
     "csrc/gemv.cu",
     "csrc/attn_decode.cu",
     "csrc/decode_step.cu",
+    "csrc/gemm_tc.cu",
+    "csrc/prefill.cu",
     "host/model.cu",
     "host/engine.cu",
     "host/safetensor.cpp",

@@ -1,0 +1,325 @@
+// Prompt-phase projections: C[M][N] = A[M][K] . B[N][K]^T on the 5th-generation tensor cores.
+//
+// Replaces kernel_standard_tiled_gemm / kernel_standard_tiled_gemm_ffn_swiglu of the reference
+// (inference.cu:393-519) for M > 1 rows, with the same FP16 inputs, FP32 accumulation and FP16
+// rounding points, and the neighbouring element-wise kernels fused into the epilogue.
+//
+// Bound: tensor pipe (2 * M * N * K flops); A and B are both K-major, which is how the
+// activations and the checkpoint's [out][in] weights already sit in memory.
+//
+//   tile     128 x 128 output per CTA, K in steps of 64 (one 128-byte swizzle span of FP16)
+//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast) fills a 4-stage
+//            shared-memory ring, completion on mbarriers
+//   warp 1   allocates tensor memory and issues tcgen05.mma (kind::f16, M = 128, N = 128, K = 16)
+//            from one elected lane; tcgen05.commit releases ring stages and signals the epilogue
+//   warps 2-5 epilogue: tcgen05.ld the FP32 accumulators (one output row per thread), apply
+//            store / residual add / RoPE + KV-cache append / SiLU(gate) * up, write FP16
+// The SwiGLU variant keeps two accumulators (gate and up, 2 x 128 TMEM columns) fed by two B tiles.
+// Rows of A beyond M are zero-filled by TMA and masked in the epilogue; N and K must be multiples
+// of 128 and 64.  Every mbarrier wait is bounded (status word, see llmb_device_status).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace llmb {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64, kGemmStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kTileBytes = kBM * kBK * 2;  // 16 KB: one A or B tile of a stage
+
+struct GemmParams {
+    __half *c;              // STORE/RESIDUAL/SWIGLU: [M][N] (SWIGLU: N = ffn); ROPE_KV: q [M][n_q]
+    const float2 *rope_cs;  // ROPE_KV: [M][head_dim / 2]
+    __half *k_cache, *v_cache;
+    int *status;
+    int M, N, K, epilogue;
+    int n_q, n_kv, head_dim, pos0, max_pos;
+};
+
+__device__ __forceinline__ uint64_t umma_desc(const void *smem_tile) {
+    // K-major, 128-byte swizzle: rows are 128 bytes, 8-row groups are 1024 bytes apart (SBO);
+    // descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+    const uint64_t addr = smem_u32(smem_tile);
+    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float silu_gemm(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
+
+template <bool DUAL>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char gemm_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kGemmStages];
+    __shared__ __align__(8) uint64_t empty_bar[kGemmStages];
+    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int prior_status;
+
+    constexpr uint32_t kStageBytes = (DUAL ? 3 : 2) * kTileBytes;
+    constexpr uint32_t kTmemCols = DUAL ? 256 : 128;
+    // kind::f16: D = F32 (bit 4), A = B = F16 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+    // the dynamic shared memory window is only 16-byte aligned by contract: align the ring to 1024 bytes
+    unsigned char *ring = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+    const int k_tiles = p.K / kBK;
+
+    // a wait that gave up earlier (here or in another kernel) leaves the status word set: do not queue
+    // up more bounded waits behind it
+    if (threadIdx.x == 0) prior_status = *reinterpret_cast<volatile int *>(p.status);
+    __syncthreads();
+    if (prior_status != 0) return;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) {  // one warp allocates the accumulator columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < k_tiles && ok; ++kt) {
+                const int s = kt % kGemmStages;
+                if (kt >= kGemmStages) ok = mbar_wait(&empty_bar[s], ((kt / kGemmStages) - 1) & 1, p.status, 301);
+                if (!ok) break;
+                unsigned char *st = ring + (size_t)s * kStageBytes;
+                mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+                tma_load_2d(st, &map_a, kt * kBK, m0, &full_bar[s]);
+                tma_load_2d(st + kTileBytes, &map_b, kt * kBK, n0, &full_bar[s]);
+                if (DUAL) tma_load_2d(st + 2 * kTileBytes, &map_b2, kt * kBK, n0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < k_tiles && ok; ++kt) {
+                const int s = kt % kGemmStages;
+                ok = mbar_wait(&full_bar[s], (kt / kGemmStages) & 1, p.status, 302);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char *st = ring + (size_t)s * kStageBytes;
+                const uint64_t adesc = umma_desc(st), bdesc = umma_desc(st + kTileBytes);
+                const uint64_t b2desc = DUAL ? umma_desc(st + 2 * kTileBytes) : 0;
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) {
+                    const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
+                    // 16 FP16 along K = 32 bytes = 2 descriptor address units inside the swizzle span
+                    umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+                    if (DUAL) umma_f16(tmem_base + kBN, adesc + 2 * k, b2desc + 2 * k, kIdesc, acc);
+                }
+                umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(&acc_bar);  // arrives even after a failed wait, so the epilogue never waits forever
+        }
+    } else {
+        // ---- epilogue: thread = one row of the tile, TMEM lanes (warp % 4) * 32 .. + 32 ----
+        const bool ok = mbar_wait(&acc_bar, 0, p.status, 303);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int lane_group = (warp & 3) * 32;
+        const int row = m0 + lane_group + lane;
+        const bool row_ok = ok && row < p.M;
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+            uint32_t v[32], u[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16) + (uint32_t)(c * 32);
+            tmem_ld32(taddr, v);
+            if (DUAL) tmem_ld32(taddr + kBN, u);
+            if (!row_ok) continue;
+            const int col0 = n0 + c * 32;
+            __align__(16) __half out[32];
+            if (DUAL) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) out[i] = __float2half_rn(silu_gemm(__uint_as_float(v[i])) * __uint_as_float(u[i]));
+                uint4 *dst = reinterpret_cast<uint4 *>(p.c + (size_t)row * p.N + col0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = reinterpret_cast<const uint4 *>(out)[i];
+            } else if (p.epilogue == LLMB_EPI_STORE) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) out[i] = __float2half_rn(__uint_as_float(v[i]));
+                uint4 *dst = reinterpret_cast<uint4 *>(p.c + (size_t)row * p.N + col0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = reinterpret_cast<const uint4 *>(out)[i];
+            } else if (p.epilogue == LLMB_EPI_RESIDUAL) {
+                uint4 *dst = reinterpret_cast<uint4 *>(p.c + (size_t)row * p.N + col0);
+                __align__(16) __half res[32];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<uint4 *>(res)[i] = dst[i];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    out[i] = __float2half_rn(__half2float(__float2half_rn(__uint_as_float(v[i]))) + __half2float(res[i]));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = reinterpret_cast<const uint4 *>(out)[i];
+            } else {  // LLMB_EPI_ROPE_KV
+                const int pos = p.pos0 + row;
+                const int half_dim = p.head_dim >> 1;
+                const bool is_v = col0 >= p.n_q + p.n_kv;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float e = __half2float(__float2half_rn(__uint_as_float(v[i])));
+                    const float o = __half2float(__float2half_rn(__uint_as_float(v[i + 1])));
+                    if (is_v) {
+                        out[i] = __float2half_rn(__uint_as_float(v[i]));
+                        out[i + 1] = __float2half_rn(__uint_as_float(v[i + 1]));
+                    } else {
+                        const int local = (col0 < p.n_q ? col0 : col0 - p.n_q) + i;
+                        const float2 cs = p.rope_cs[(size_t)row * half_dim + ((local >> 1) % half_dim)];
+                        out[i] = __float2half_rn(__fmaf_rn(cs.x, e, -__fmul_rn(cs.y, o)));
+                        out[i + 1] = __float2half_rn(__fmaf_rn(cs.y, e, __fmul_rn(cs.x, o)));
+                    }
+                }
+                __half *dstp = nullptr;
+                if (col0 < p.n_q) dstp = p.c + (size_t)row * p.n_q + col0;
+                else if (pos >= 0 && pos < p.max_pos)
+                    dstp = (is_v ? p.v_cache + (size_t)pos * p.n_kv + (col0 - p.n_q - p.n_kv)
+                                 : p.k_cache + (size_t)pos * p.n_kv + (col0 - p.n_q));
+                if (dstp) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) reinterpret_cast<uint4 *>(dstp)[i] = reinterpret_cast<const uint4 *>(out)[i];
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [rows][k] FP16 row-major as a 2-D tensor map with a 64 x 128 box and 128-byte swizzle.
+static int make_map(CUtensorMap *map, const void *base, int rows, int k) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_last_error("cuTensorMapEncodeTiled is not available from this driver");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed (base must be 16-byte aligned, k a multiple of 8)");
+        return LLMB_ERR_INVALID;
+    }
+    return LLMB_OK;
+}
+
+}  // namespace llmb
+
+extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
+    using namespace llmb;
+    if (!a || !a->a || !a->b || !a->c || a->m <= 0 || a->n <= 0 || a->k <= 0) return LLMB_ERR_INVALID;
+    if (a->n % kBN || a->k % kBK) {
+        set_last_error("llmb_gemm_f16: n must be a multiple of 128 and k a multiple of 64");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    const bool dual = a->epilogue == LLMB_EPI_SWIGLU;
+    if (dual && !a->b2) return LLMB_ERR_INVALID;
+    if (a->epilogue == LLMB_EPI_ROPE_KV) {
+        if (!a->rope_cs || !a->k_cache || !a->v_cache || a->head_dim <= 0 || (a->head_dim & 1) ||
+            a->n != a->n_q + 2 * a->n_kv || a->n_q % 32 || a->n_kv % 32)
+            return LLMB_ERR_INVALID;
+    } else if (a->epilogue != LLMB_EPI_STORE && a->epilogue != LLMB_EPI_RESIDUAL && !dual) {
+        return LLMB_ERR_INVALID;
+    }
+    CUtensorMap ma, mb, mb2;
+    int rc;
+    if ((rc = make_map(&ma, a->a, a->m, a->k))) return rc;
+    if ((rc = make_map(&mb, a->b, a->n, a->k))) return rc;
+    if ((rc = make_map(&mb2, dual ? a->b2 : a->b, a->n, a->k))) return rc;
+    GemmParams p = {};
+    p.c = reinterpret_cast<__half *>(a->c);
+    p.rope_cs = reinterpret_cast<const float2 *>(a->rope_cs);
+    p.k_cache = reinterpret_cast<__half *>(a->k_cache);
+    p.v_cache = reinterpret_cast<__half *>(a->v_cache);
+    p.status = device_status_ptr();
+    if (!p.status) return LLMB_ERR_CUDA;
+    p.M = a->m; p.N = a->n; p.K = a->k; p.epilogue = a->epilogue;
+    p.n_q = a->n_q; p.n_kv = a->n_kv; p.head_dim = a->head_dim; p.pos0 = a->pos0; p.max_pos = a->max_pos;
+    const size_t smem = (size_t)kGemmStages * (dual ? 3 : 2) * kTileBytes + 1024;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    dim3 grid(a->n / kBN, (a->m + kBM - 1) / kBM);
+    static bool attr[2] = {false, false};
+    if (dual) {
+        if (!attr[1]) {
+            LLMB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr[1] = true;
+        }
+        gemm_tc_kernel<true><<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
+    } else {
+        if (!attr[0]) {
+            LLMB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr[0] = true;
+        }
+        gemm_tc_kernel<false><<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
+    }
+    LLMB_CUDA_OK(cudaGetLastError());
+    return LLMB_OK;
+}

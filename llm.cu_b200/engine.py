@@ -81,6 +81,11 @@ class Cache:
         if step_kernel >= 0:
             check(lib.cache_use_step_kernel(self.ptr, int(step_kernel)), "cache_use_step_kernel")
 
+    def set_prefill(self, enable=True, min_rows=0):
+        """Prompt tokens as blocks of rows through the tensor-core projections (default), or one by one
+        through the decode step; `min_rows` > 0 changes the smallest run that takes the block path."""
+        check(lib.cache_set_prefill(self.ptr, 1 if enable else 0, int(min_rows)), "cache_set_prefill")
+
     def tp_connect(self, group=None):
         """Exchanges the CUDA IPC handles of the ranks' exchange blocks over torch.distributed and maps the
         peers' blocks (one process per GPU; every rank calls this once before the first step)."""

@@ -21,6 +21,7 @@
 //
 // KV cache: K and V are [n_layers][max_seq][n_kv_heads * head_dim] FP16, K stored after RoPE:
 // the reference's row layout (inference.cu:761-768, :926) with a layer axis added.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -75,6 +76,12 @@ struct Engine {
     std::map<int, cudaGraphExec_t> graphs;  // key: bucket * 2 + with_logits
     long long launches = 0;
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    // prompt phase: blocks of rows through the tensor-core projections
+    bool batched_prefill = true;
+    int prefill_min_rows = 16, prefill_chunk = 1024, pf_rows = 0;
+    __half *pf_x = nullptr, *pf_xn = nullptr, *pf_q = nullptr, *pf_attn = nullptr, *pf_h = nullptr;
+    float *pf_rope = nullptr;
+    int *pf_pos = nullptr;
 };
 
 inline Engine *eng(const CudaCache *c) { return c ? static_cast<Engine *>(c->priv) : nullptr; }
@@ -286,6 +293,107 @@ int set_device_int(Engine *e, int *dst, int value) {
     return LLMB_OK;
 }
 
+// The block path needs tile-aligned projection shapes and all of the model on this GPU.
+bool prefill_supported(const Engine *e) {
+    const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    return e->tp_size == 1 && !e->hidden_dump && (e->hd == 64 || e->hd == 128) && (n_q + 2 * n_kv) % 128 == 0 &&
+           e->d % 128 == 0 && e->ffn % 128 == 0 && n_q % 64 == 0 && n_kv % 32 == 0;
+}
+
+void free_prefill_buffers(Engine *e) {
+    cudaFree(e->pf_x); cudaFree(e->pf_xn); cudaFree(e->pf_q); cudaFree(e->pf_attn); cudaFree(e->pf_h);
+    cudaFree(e->pf_rope); cudaFree(e->pf_pos);
+    e->pf_x = e->pf_xn = e->pf_q = e->pf_attn = e->pf_h = nullptr;
+    e->pf_rope = nullptr;
+    e->pf_pos = nullptr;
+    e->pf_rows = 0;
+}
+
+int ensure_prefill_buffers(Engine *e, int rows) {
+    if (rows <= e->pf_rows) return LLMB_OK;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    free_prefill_buffers(e);
+    const size_t n_q = (size_t)e->nq * e->hd;
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_x, (size_t)rows * e->d * 2));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_xn, (size_t)rows * e->d * 2));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_q, (size_t)rows * n_q * 2));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_attn, (size_t)rows * n_q * 2));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_h, (size_t)rows * e->ffn * 2));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_rope, (size_t)rows * e->hd * sizeof(float)));
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_pos, (size_t)rows * sizeof(int)));
+    e->pf_rows = rows;
+    return LLMB_OK;
+}
+
+// Appends the K/V rows of history positions [from, to) to the cache, a block of rows at a time:
+// the reference's layer loop (inference.cu:157-186) with every projection a tensor-core GEMM over
+// the block.  No logits: the caller runs the last prompt token through the decode step.
+int prefill_rows(Engine *e, int from, int to) {
+    Llama3 *m = e->model;
+    const Llama3Config &c = m->config;
+    cudaStream_t s = e->stream;
+    const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    int rc = ensure_prefill_buffers(e, std::min(to - from, e->prefill_chunk));
+    if (rc) return rc;
+    auto u16 = [](const void *p) { return reinterpret_cast<const uint16_t *>(p); };
+    auto u16w = [](void *p) { return reinterpret_cast<uint16_t *>(p); };
+    for (int p0 = from; p0 < to; p0 += e->prefill_chunk) {
+        const int rows = std::min(e->prefill_chunk, to - p0);
+        if ((rc = llmb_iota_i32(e->pf_pos, p0, rows, s))) return rc;
+        if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), e->d_history + p0, e->pf_pos, rows, e->d,
+                                  e->embed_rows, e->hd, c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 0, s)))
+            return rc;
+        for (int l = 0; l < e->layers; ++l) {
+            const Llama3Layer *L = m->layers[l];
+            __half *kl = e->kcache + (size_t)l * e->max_seq * n_kv;
+            __half *vl = e->vcache + (size_t)l * e->max_seq * n_kv;
+            if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), rows, e->d,
+                                        c.eps, s)))
+                return rc;
+            LlmbGemmArgs g = {};
+            g.a = u16(e->pf_xn);
+            g.b = u16(L->self_attn_q_proj->d_fp16_tensor);  // q, k, v rows are one contiguous buffer
+            g.c = u16w(e->pf_q);
+            g.m = rows; g.n = n_q + 2 * n_kv; g.k = e->d;
+            g.epilogue = LLMB_EPI_ROPE_KV;
+            g.n_q = n_q; g.n_kv = n_kv; g.head_dim = e->hd;
+            g.rope_cs = e->pf_rope;
+            g.k_cache = u16w(kl); g.v_cache = u16w(vl);
+            g.pos0 = p0; g.max_pos = e->max_seq;
+            if ((rc = llmb_gemm_f16(&g, s))) return rc;
+            if ((rc = llmb_attn_prefill(u16(e->pf_q), u16(kl), u16(vl), rows, p0, e->nq, e->nkv, e->hd, u16w(e->pf_attn), s)))
+                return rc;
+            LlmbGemmArgs o = {};
+            o.a = u16(e->pf_attn);
+            o.b = u16(L->self_attn_o_proj->d_fp16_tensor);
+            o.c = u16w(e->pf_x);
+            o.m = rows; o.n = e->d; o.k = n_q;
+            o.epilogue = LLMB_EPI_RESIDUAL;
+            if ((rc = llmb_gemm_f16(&o, s))) return rc;
+            if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->post_attention_layernorm->d_fp16_tensor), u16w(e->pf_xn), rows,
+                                        e->d, c.eps, s)))
+                return rc;
+            LlmbGemmArgs f = {};
+            f.a = u16(e->pf_xn);
+            f.b = u16(L->mlp_gate_proj->d_fp16_tensor);
+            f.b2 = u16(L->mlp_up_proj->d_fp16_tensor);
+            f.c = u16w(e->pf_h);
+            f.m = rows; f.n = e->ffn; f.k = e->d;
+            f.epilogue = LLMB_EPI_SWIGLU;
+            if ((rc = llmb_gemm_f16(&f, s))) return rc;
+            LlmbGemmArgs dn = {};
+            dn.a = u16(e->pf_h);
+            dn.b = u16(L->mlp_down_proj->d_fp16_tensor);
+            dn.c = u16w(e->pf_x);
+            dn.m = rows; dn.n = e->d; dn.k = e->ffn;
+            dn.epilogue = LLMB_EPI_RESIDUAL;
+            if ((rc = llmb_gemm_f16(&dn, s))) return rc;
+        }
+        e->launches += 2 + 7 * e->layers;
+    }
+    return LLMB_OK;
+}
+
 // Feeds ids[from..to) (history rows from..to-1), logits only for the last one.
 int feed_tokens(Engine *e, const int *ids, int from, int to) {
     if (to <= from) return LLMB_ERR_INVALID;
@@ -296,9 +404,14 @@ int feed_tokens(Engine *e, const int *ids, int from, int to) {
     // pageable source: the runtime stages it before returning, so `ids` may change afterwards
     LLMB_CUDA_OK(cudaMemcpyAsync(e->d_history + from, ids + from, sizeof(int) * (size_t)(to - from),
                                  cudaMemcpyHostToDevice, e->stream));
-    int rc = set_device_int(e, e->d_pos, from);
-    if (rc) return rc;
-    for (int p = from; p < to; ++p)
+    int rc, first = from;
+    // all but the last token as blocks of rows; the last one through the decode step, for its logits
+    if (e->batched_prefill && to - 1 - from >= e->prefill_min_rows && prefill_supported(e)) {
+        if ((rc = prefill_rows(e, from, to - 1))) return rc;
+        first = to - 1;
+    }
+    if ((rc = set_device_int(e, e->d_pos, first))) return rc;
+    for (int p = first; p < to; ++p)
         if ((rc = run_step(e, p == to - 1, p + 1))) return rc;
     return LLMB_OK;
 }
@@ -330,6 +443,7 @@ void destroy_engine(Engine *e) {
     for (int r = 0; r < e->tp_size; ++r)
         if (e->tp_connected && r != e->tp_rank && e->peers[r]) cudaIpcCloseMemHandle(e->peers[r]);
     cudaFree(e->exchange); cudaFree(e->x_alt); cudaFree(e->trace);
+    free_prefill_buffers(e);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -611,6 +725,14 @@ extern "C" int cache_debug_read(CudaCache *cache, int which, void *out, size_t b
     if (!src) return LLMB_ERR_INVALID;
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
     LLMB_CUDA_OK(cudaMemcpy(out, src, bytes, cudaMemcpyDeviceToHost));
+    return LLMB_OK;
+}
+
+extern "C" int cache_set_prefill(CudaCache *cache, int enable, int min_rows) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    e->batched_prefill = enable != 0;
+    if (min_rows > 0) e->prefill_min_rows = min_rows;
     return LLMB_OK;
 }
 

@@ -46,3 +46,9 @@ def oracle():
 @pytest.fixture(scope="session")
 def tiny_weights(pkg, oracle):
     return oracle.Weights(pkg.CONFIGS["tiny"], seed=0)
+
+
+@pytest.fixture(scope="session")
+def weights_8b_l2(pkg, oracle):
+    """LLaMA3-8B layer shape, two layers, 1024 embedding rows: the shape pinned against the reference."""
+    return oracle.Weights(pkg.CONFIGS["llama3_8b_l2"], seed=0, keep_file=False)

@@ -134,11 +134,6 @@ def test_bf16_load_conversion_model(pkg, oracle):
     model.close()
 
 
-@pytest.fixture(scope="module")
-def weights_8b_l2(pkg, oracle):
-    return oracle.Weights(pkg.CONFIGS["llama3_8b_l2"], seed=0, keep_file=False)
-
-
 @pytest.mark.parametrize("step_kernel", [1, 0])
 def test_8b_layer_shapes_two_layers(pkg, oracle, weights_8b_l2, step_kernel):
     """LLaMA3-8B layer shape (d 4096, 32/8 heads, ffn 14336, vocab 128256), two layers."""

@@ -1,0 +1,255 @@
+"""Prompt-phase kernels (tensor-core GEMM with fused epilogues, row RMSNorm, block attention) through
+the C-ABI, and the engine's block prefill against the token-by-token path and the CPU oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+from gpu_util import assert_close_fp16, dev, f16, host_u16, rmsnorm_ref, to_f16_bits  # noqa: E402
+
+EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+
+
+def check_status(pkg):
+    st = C.c_int(-1)
+    assert pkg.lib.llmb_device_status(C.byref(st)) == 0, pkg.lib.llmb_last_error()
+    assert st.value == 0, "device status %d" % st.value
+
+
+def gemm(pkg, **kw):
+    a = pkg.GemmArgs()
+    for k, v in kw.items():
+        setattr(a, k, v.data_ptr() if hasattr(v, "data_ptr") else v)
+    rc = pkg.lib.llmb_gemm_f16(C.byref(a), None)
+    assert rc == 0, (rc, pkg.lib.llmb_last_error())
+    torch.cuda.synchronize()
+    check_status(pkg)
+
+
+def mats(oracle, m, n, k, seed=0):
+    a = oracle.synth_fp16(900 + seed, 1, m * k, std=1.0).reshape(m, k)
+    b = oracle.synth_fp16(900 + seed, 2, n * k, std=0.02).reshape(n, k)
+    return a, b
+
+
+def matmul64(a_bits, b_bits):
+    return f16(a_bits).astype(np.float64) @ f16(b_bits).astype(np.float64).T
+
+
+def tc_tol(want, k):
+    """Absolute tolerance of a tensor-core FP32 accumulation over k terms: the MMA aligns its addends to
+    the largest exponent and truncates, so the error grows with k times 2^-24 of the running magnitude
+    instead of with the FP32 rounding of a sequential sum.  Matters only for outputs that cancel to far
+    below the typical magnitude, where one FP16 ulp is smaller than that."""
+    return k * 2.0 ** -23 * float(np.abs(want).max())
+
+
+def test_epilogue_constants_match_header(pkg):
+    import re, os
+    hdr = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "llm_b200.h")).read()
+    for name, val in (("STORE", EPI_STORE), ("RESIDUAL", EPI_RESIDUAL), ("ROPE_KV", EPI_ROPE_KV), ("SWIGLU", EPI_SWIGLU)):
+        m = re.search(r"LLMB_EPI_%s\s*=?\s*(\d+)" % name, hdr)
+        assert m and int(m.group(1)) == val, name
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (16, 256, 256), (200, 384, 768), (300, 512, 4096), (1, 128, 128)])
+def test_gemm_store(pkg, oracle, m, n, k):
+    a, b = mats(oracle, m, n, k)
+    out = torch.full((m + 3, n), 0x7BFF, dtype=torch.int16, device="cuda")  # rows past m must stay untouched
+    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_STORE)
+    got = host_u16(out)
+    want = matmul64(a, b)
+    print("gemm %dx%dx%d: max abs err %.3g" % (m, n, k, np.abs(f16(got[:m]) - want).max()))
+    assert_close_fp16(got[:m], want, what="gemm %dx%dx%d" % (m, n, k), abs_tol=tc_tol(want, k))
+    assert (got[m:] == 0x7BFF).all()
+
+
+def test_gemm_residual(pkg, oracle):
+    m, n, k = 150, 256, 512
+    a, b = mats(oracle, m, n, k, 1)
+    res = oracle.synth_fp16(7, 3, m * n, std=1.0).reshape(m, n)
+    out = dev(res.copy())
+    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_RESIDUAL)
+    acc = matmul64(a, b)
+    want = acc.astype(np.float16).astype(np.float64) + f16(res).astype(np.float64)
+    # half(acc) may sit one FP16 ulp from the FP64 product's rounding; after the add cancels, that ulp of
+    # the product is many ulps of a small sum
+    assert_close_fp16(host_u16(out).reshape(m, n), want, what="gemm residual", max_frac=0.1,
+                      abs_tol=np.abs(acc) * 2.0 ** -10 + tc_tol(acc, k))
+
+
+def test_gemm_swiglu(pkg, oracle):
+    m, n, k = 130, 384, 256
+    a, b = mats(oracle, m, n, k, 2)
+    b2 = oracle.synth_fp16(8, 4, n * k, std=0.02).reshape(n, k)
+    out = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+    gemm(pkg, a=dev(a), b=dev(b), b2=dev(b2), c=out, m=m, n=n, k=k, epilogue=EPI_SWIGLU)
+    g, u = matmul64(a, b), matmul64(a, b2)
+    want = g / (1.0 + np.exp(-g)) * u
+    assert_close_fp16(host_u16(out).reshape(m, n), want, what="gemm swiglu", abs_tol=tc_tol(want, k))
+
+
+def test_gemm_rope_kv(pkg, oracle):
+    hd, nqh, nkvh, k, m, pos0, max_pos = 64, 4, 2, 256, 70, 5, 128
+    n_q, n_kv = nqh * hd, nkvh * hd
+    n = n_q + 2 * n_kv
+    a, b = mats(oracle, m, n, k, 3)
+    pos = np.arange(pos0, pos0 + m, dtype=np.float32)
+    i = np.arange(hd // 2, dtype=np.float32)
+    freq = (1.0 / np.power(np.float32(500000.0), 2.0 * i / np.float32(hd))).astype(np.float32)
+    ang = (pos[:, None] * freq[None, :]).astype(np.float32)
+    cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)  # [m][hd/2][2]
+    q_out = torch.zeros((m, n_q), dtype=torch.int16, device="cuda")
+    kc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
+    vc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
+    gemm(pkg, a=dev(a), b=dev(b), c=q_out, m=m, n=n, k=k, epilogue=EPI_ROPE_KV, n_q=n_q, n_kv=n_kv, head_dim=hd,
+         rope_cs=dev(cs), k_cache=kc, v_cache=vc, pos0=pos0, max_pos=max_pos)
+    y = matmul64(a, b).astype(np.float16).astype(np.float64)
+
+    def rope(block, heads):
+        r = block.reshape(m, heads, hd // 2, 2)
+        c, s = cs[:, None, :, 0].astype(np.float64), cs[:, None, :, 1].astype(np.float64)
+        out = np.empty_like(r)
+        out[..., 0] = c * r[..., 0] - s * r[..., 1]
+        out[..., 1] = s * r[..., 0] + c * r[..., 1]
+        return out.reshape(m, heads * hd)
+
+    def pair_tol(block):
+        """One FP16 ulp of either input of a rotated pair (the projection is rounded to FP16 before RoPE)."""
+        mag = np.abs(block).reshape(m, -1, 2).sum(axis=2, keepdims=True) * 2.0 ** -10
+        return np.broadcast_to(mag, (m, block.shape[1] // 2, 2)).reshape(m, -1) + tc_tol(y, k)
+
+    assert_close_fp16(host_u16(q_out).reshape(m, n_q), rope(y[:, :n_q], nqh), what="q rope", max_frac=0.1,
+                      abs_tol=pair_tol(y[:, :n_q]))
+    kgot, vgot = host_u16(kc).reshape(max_pos, n_kv), host_u16(vc).reshape(max_pos, n_kv)
+    assert_close_fp16(kgot[pos0:pos0 + m], rope(y[:, n_q:n_q + n_kv], nkvh), what="k rope", max_frac=0.1,
+                      abs_tol=pair_tol(y[:, n_q:n_q + n_kv]))
+    assert_close_fp16(vgot[pos0:pos0 + m], y[:, n_q + n_kv:], what="v", abs_tol=tc_tol(y, k))
+    assert not kgot[:pos0].any() and not kgot[pos0 + m:].any() and not vgot[:pos0].any() and not vgot[pos0 + m:].any()
+
+
+def test_gemm_rejects_unaligned_shapes(pkg):
+    t = torch.zeros(1 << 16, dtype=torch.int16, device="cuda")
+    a = pkg.GemmArgs(a=t.data_ptr(), b=t.data_ptr(), c=t.data_ptr(), m=4, n=100, k=64, epilogue=EPI_STORE)
+    assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
+    a = pkg.GemmArgs(a=t.data_ptr(), b=t.data_ptr(), c=t.data_ptr(), m=4, n=128, k=40, epilogue=EPI_STORE)
+    assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
+    a = pkg.GemmArgs(a=t.data_ptr(), b=t.data_ptr(), c=t.data_ptr(), m=0, n=128, k=64, epilogue=EPI_STORE)
+    assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
+
+
+@pytest.mark.parametrize("m,d", [(5, 256), (33, 4096), (3, 1000)])
+def test_rmsnorm_rows_bit_exact(pkg, oracle, m, d):
+    x = oracle.synth_fp16(11, 1, m * d, std=1.0).reshape(m, d)
+    g = oracle.synth_fp16(11, 2, d, std=1.0)
+    y = torch.zeros((m, d), dtype=torch.int16, device="cuda")
+    dx, dg = dev(x), dev(g)
+    assert pkg.lib.llmb_rmsnorm_rows(dx.data_ptr(), dg.data_ptr(), y.data_ptr(), m, d, 1e-5, None) == 0
+    got = host_u16(y).reshape(m, d)
+    for r in range(m):
+        want = rmsnorm_ref(x[r], g)
+        # the device fuses the partial's multiply-adds; a value may sit one ulp across a rounding boundary
+        assert_close_fp16(got[r], f16(want).astype(np.float64), what="rmsnorm row %d" % r)
+
+
+@pytest.mark.parametrize("hd,nqh,nkvh,m,pos0", [(64, 4, 2, 45, 0), (128, 8, 2, 70, 37), (128, 4, 4, 1, 3)])
+def test_attn_prefill_matches_fp64(pkg, oracle, hd, nqh, nkvh, m, pos0):
+    total = pos0 + m
+    n_q, n_kv = nqh * hd, nkvh * hd
+    q = oracle.synth_fp16(21, 1, m * n_q, std=1.0).reshape(m, n_q)
+    kc = oracle.synth_fp16(21, 2, (total + 4) * n_kv, std=1.0).reshape(total + 4, n_kv)
+    vc = oracle.synth_fp16(21, 3, (total + 4) * n_kv, std=1.0).reshape(total + 4, n_kv)
+    kc[total:] = 0x7E00  # rows past the causal limit hold NaN: they must never be read into the result
+    vc[total:] = 0x7E00
+    out = torch.zeros((m, n_q), dtype=torch.int16, device="cuda")
+    dq, dk, dv = dev(q), dev(kc), dev(vc)
+    rc = pkg.lib.llmb_attn_prefill(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), m, pos0, nqh, nkvh, hd,
+                                   out.data_ptr(), None)
+    assert rc == 0, pkg.lib.llmb_last_error()
+    got = host_u16(out).reshape(m, nqh, hd)
+    qf = f16(q).astype(np.float64).reshape(m, nqh, hd)
+    kf = f16(kc[:total]).astype(np.float64).reshape(total, nkvh, hd)
+    vf = f16(vc[:total]).astype(np.float64).reshape(total, nkvh, hd)
+    want = np.zeros((m, nqh, hd))
+    for h in range(nqh):
+        g = h // (nqh // nkvh)
+        s = qf[:, h] @ kf[:, g].T / np.sqrt(float(hd))
+        for r in range(m):
+            s[r, pos0 + r + 1:] = -np.inf
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        want[:, h] = (p / p.sum(axis=1, keepdims=True)) @ vf[:, g]
+    assert_close_fp16(got.reshape(m, -1), want.reshape(m, -1), what="attn prefill", max_frac=0.2, abs_tol=2e-3)
+
+
+def run_prompt(pkg, model, prompt, n_new, block, step_kernel=1):
+    cache = pkg.Cache(model)
+    cache.set_options(step_kernel=step_kernel)
+    cache.set_prefill(block, 4)
+    nxt = cache.infer(prompt)
+    logits = cache.logits()
+    launches = cache.kernel_launches()
+    toks, _, _ = cache.greedy(prompt, n_new)
+    cache.close()
+    return nxt, logits, toks, launches
+
+
+@pytest.mark.parametrize("n_prompt", [6, 40, 161])
+def test_tiny_block_prefill_matches_stepwise_and_oracle(pkg, oracle, tiny_weights, n_prompt):
+    cfg = pkg.CONFIGS["tiny"]
+    prompt = oracle.synth_tokens(3, n_prompt, cfg.vocab).tolist()
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=256)
+    a = run_prompt(pkg, model, prompt, 8, True)
+    b = run_prompt(pkg, model, prompt, 8, False)
+    ref_logits, _ = oracle.forward(tiny_weights, np.asarray(prompt, dtype=np.int32), first_logit_row=n_prompt - 1)
+    da = np.abs(oracle.f16(a[1]) - oracle.f16(ref_logits[0])).max()
+    db = np.abs(oracle.f16(b[1]) - oracle.f16(ref_logits[0])).max()
+    print("tiny prompt %d: block |dlogit| %.4g, stepwise %.4g" % (n_prompt, da, db))
+    assert da <= 2e-2 and db <= 2e-2
+    assert a[0] == b[0] and a[2] == b[2]
+    L = cfg.n_layers
+    assert a[3] == (2 + 7 * L) + 1 and b[3] == n_prompt  # one block + one decode step vs one step per token
+    model.close()
+
+
+def test_block_prefill_extends_a_cached_prefix(pkg, oracle, tiny_weights):
+    """A second inference() call that appends 30 tokens to a 50-token prefix prefills only the new rows
+    (pos0 = 50) and must agree with a fresh run on all 80."""
+    cfg = pkg.CONFIGS["tiny"]
+    ids = oracle.synth_tokens(4, 80, cfg.vocab).tolist()
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=256)
+    c1 = pkg.Cache(model)
+    c1.set_prefill(True, 4)
+    c1.infer(ids[:50])
+    n1 = c1.infer(ids)
+    l1 = c1.logits()
+    c2 = pkg.Cache(model)
+    c2.set_prefill(True, 4)
+    n2 = c2.infer(ids)
+    l2 = c2.logits()
+    assert n1 == n2
+    assert np.abs(oracle.f16(l1) - oracle.f16(l2)).max() <= 4e-3
+    c1.close(); c2.close(); model.close()
+
+
+def test_8b_layer_shapes_block_prefill(pkg, oracle, weights_8b_l2):
+    cfg = pkg.CONFIGS["llama3_8b_l2"]
+    n_prompt = 48
+    prompt = oracle.synth_tokens(0, n_prompt, cfg.embed_rows).tolist()
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=256)
+    a = run_prompt(pkg, model, prompt, 4, True)
+    ref_logits, _ = oracle.forward(weights_8b_l2, np.asarray(prompt, dtype=np.int32), first_logit_row=n_prompt - 1)
+    d = np.abs(oracle.f16(a[1]) - oracle.f16(ref_logits[0])).max()
+    print("8b_l2 block prefill: |dlogit| %.4g" % d)
+    assert d <= 2e-2
+    want_tok = int(oracle.lib().oracle_argmax_fp16(ref_logits[0].ctypes.data, len(ref_logits[0])))
+    assert a[0] == want_tok
+    model.close()
