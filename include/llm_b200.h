@@ -196,6 +196,7 @@ typedef struct {
     uint16_t *v_cache;
     int pos0;              /* cache row of A's row 0 */
     int max_pos;
+    int tile_n;            /* output columns per CTA: 0 = the widest of 128/64/32 that fills the SMs */
 } LlmbGemmArgs;
 
 int llmb_gemm_f16(const LlmbGemmArgs *args, llmb_stream_t stream);

@@ -7,14 +7,16 @@
 // Bound: tensor pipe (2 * M * N * K flops); A and B are both K-major, which is how the
 // activations and the checkpoint's [out][in] weights already sit in memory.
 //
-//   tile     128 x 128 output per CTA, K in steps of 64 (one 128-byte swizzle span of FP16)
-//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast) fills a 4-stage
-//            shared-memory ring, completion on mbarriers
-//   warp 1   allocates tensor memory and issues tcgen05.mma (kind::f16, M = 128, N = 128, K = 16)
+//   tile     128 x BN output per CTA (BN = 128, 64 or 32: the widest that still gives every SM a CTA),
+//            K in steps of 64 (one 128-byte swizzle span of FP16); two CTAs share an SM, so one's
+//            epilogue overlaps the other's main loop
+//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast) fills a 3-stage
+//            (SwiGLU: 2-stage) shared-memory ring, completion on mbarriers
+//   warp 1   allocates tensor memory and issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16)
 //            from one elected lane; tcgen05.commit releases ring stages and signals the epilogue
 //   warps 2-5 epilogue: tcgen05.ld the FP32 accumulators (one output row per thread), apply
 //            store / residual add / RoPE + KV-cache append / SiLU(gate) * up, write FP16
-// The SwiGLU variant keeps two accumulators (gate and up, 2 x 128 TMEM columns) fed by two B tiles.
+// The SwiGLU variant keeps two accumulators (gate and up, 2 x BN TMEM columns) fed by two B tiles.
 // Rows of A beyond M are zero-filled by TMA and masked in the epilogue; N and K must be multiples
 // of 128 and 64.  Every mbarrier wait is bounded (status word, see llmb_device_status).
 #include <cuda.h>
@@ -23,9 +25,11 @@
 
 namespace llmb {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64, kGemmStages = 4;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kGemmThreads = 192;
-constexpr uint32_t kTileBytes = kBM * kBK * 2;  // 16 KB: one A or B tile of a stage
+constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 16 KB: the A tile of a stage
+__host__ __device__ constexpr int gemm_stages(bool dual) { return dual ? 2 : 3; }
+__host__ __device__ constexpr uint32_t gemm_stage_bytes(bool dual, int bn) { return kATileBytes + (dual ? 2 : 1) * bn * kBK * 2; }
 
 struct GemmParams {
     __half *c;              // STORE/RESIDUAL/SWIGLU: [M][N] (SWIGLU: N = ffn); ROPE_KV: q [M][n_q]
@@ -78,26 +82,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 __device__ __forceinline__ float silu_gemm(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
 
-template <bool DUAL>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <bool DUAL, int kBN>
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
     extern __shared__ __align__(1024) unsigned char gemm_smem[];
-    __shared__ __align__(8) uint64_t full_bar[kGemmStages];
-    __shared__ __align__(8) uint64_t empty_bar[kGemmStages];
+    __shared__ __align__(8) uint64_t full_bar[gemm_stages(DUAL)];
+    __shared__ __align__(8) uint64_t empty_bar[gemm_stages(DUAL)];
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int prior_status;
 
-    constexpr uint32_t kStageBytes = (DUAL ? 3 : 2) * kTileBytes;
-    constexpr uint32_t kTmemCols = DUAL ? 256 : 128;
+    constexpr int kGemmStages = gemm_stages(DUAL);
+    constexpr uint32_t kBTileBytes = kBN * kBK * 2;
+    constexpr uint32_t kStageBytes = gemm_stage_bytes(DUAL, kBN);  // every tile a multiple of 1024 bytes
+    constexpr uint32_t kTmemCols = (DUAL ? 2 : 1) * kBN < 32 ? 32 : (DUAL ? 2 : 1) * kBN;
     // kind::f16: D = F32 (bit 4), A = B = F16 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 
     // the dynamic shared memory window is only 16-byte aligned by contract: align the ring to 1024 bytes
     unsigned char *ring = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+    // row tiles vary fastest across the grid: the CTAs that share a weight tile run together and it
+    // comes from DRAM once
+    const int m0 = blockIdx.x * kBM, n0 = blockIdx.y * kBN;
     const int k_tiles = p.K / kBK;
 
     // a wait that gave up earlier (here or in another kernel) leaves the status word set: do not queue
@@ -132,8 +140,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 unsigned char *st = ring + (size_t)s * kStageBytes;
                 mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
                 tma_load_2d(st, &map_a, kt * kBK, m0, &full_bar[s]);
-                tma_load_2d(st + kTileBytes, &map_b, kt * kBK, n0, &full_bar[s]);
-                if (DUAL) tma_load_2d(st + 2 * kTileBytes, &map_b2, kt * kBK, n0, &full_bar[s]);
+                tma_load_2d(st + kATileBytes, &map_b, kt * kBK, n0, &full_bar[s]);
+                if (DUAL) tma_load_2d(st + kATileBytes + kBTileBytes, &map_b2, kt * kBK, n0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
@@ -145,8 +153,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned char *st = ring + (size_t)s * kStageBytes;
-                const uint64_t adesc = umma_desc(st), bdesc = umma_desc(st + kTileBytes);
-                const uint64_t b2desc = DUAL ? umma_desc(st + 2 * kTileBytes) : 0;
+                const uint64_t adesc = umma_desc(st), bdesc = umma_desc(st + kATileBytes);
+                const uint64_t b2desc = DUAL ? umma_desc(st + kATileBytes + kBTileBytes) : 0;
 #pragma unroll
                 for (int k = 0; k < kBK / 16; ++k) {
                     const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
@@ -250,8 +258,8 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [rows][k] FP16 row-major as a 2-D tensor map with a 64 x 128 box and 128-byte swizzle.
-static int make_map(CUtensorMap *map, const void *base, int rows, int k) {
+// [rows][k] FP16 row-major as a 2-D tensor map with a 64 x box_rows box and 128-byte swizzle.
+static int make_map(CUtensorMap *map, const void *base, int rows, int k, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_last_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -259,7 +267,7 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int k) {
     }
     const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -276,7 +284,7 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int k) {
 extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     using namespace llmb;
     if (!a || !a->a || !a->b || !a->c || a->m <= 0 || a->n <= 0 || a->k <= 0) return LLMB_ERR_INVALID;
-    if (a->n % kBN || a->k % kBK) {
+    if (a->n % 128 || a->k % kBK) {
         set_last_error("llmb_gemm_f16: n must be a multiple of 128 and k a multiple of 64");
         return LLMB_ERR_UNSUPPORTED;
     }
@@ -289,11 +297,22 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     } else if (a->epilogue != LLMB_EPI_STORE && a->epilogue != LLMB_EPI_RESIDUAL && !dual) {
         return LLMB_ERR_INVALID;
     }
+    // the widest tile that still gives every SM a CTA
+    const int m_tiles = (a->m + kBM - 1) / kBM;
+    int bn = a->tile_n;
+    if (bn == 0) {
+        bn = 128;
+        while (bn > 32 && (a->n / bn) * m_tiles < sm_count_cached()) bn >>= 1;
+    }
+    if (bn != 128 && bn != 64 && bn != 32) {
+        set_last_error("llmb_gemm_f16: tile_n must be 0, 32, 64 or 128");
+        return LLMB_ERR_INVALID;
+    }
     CUtensorMap ma, mb, mb2;
     int rc;
-    if ((rc = make_map(&ma, a->a, a->m, a->k))) return rc;
-    if ((rc = make_map(&mb, a->b, a->n, a->k))) return rc;
-    if ((rc = make_map(&mb2, dual ? a->b2 : a->b, a->n, a->k))) return rc;
+    if ((rc = make_map(&ma, a->a, a->m, a->k, kBM))) return rc;
+    if ((rc = make_map(&mb, a->b, a->n, a->k, bn))) return rc;
+    if ((rc = make_map(&mb2, dual ? a->b2 : a->b, a->n, a->k, bn))) return rc;
     GemmParams p = {};
     p.c = reinterpret_cast<__half *>(a->c);
     p.rope_cs = reinterpret_cast<const float2 *>(a->rope_cs);
@@ -303,23 +322,19 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     if (!p.status) return LLMB_ERR_CUDA;
     p.M = a->m; p.N = a->n; p.K = a->k; p.epilogue = a->epilogue;
     p.n_q = a->n_q; p.n_kv = a->n_kv; p.head_dim = a->head_dim; p.pos0 = a->pos0; p.max_pos = a->max_pos;
-    const size_t smem = (size_t)kGemmStages * (dual ? 3 : 2) * kTileBytes + 1024;
+    const size_t smem = (size_t)gemm_stages(dual) * gemm_stage_bytes(dual, bn) + 1024;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    dim3 grid(a->n / kBN, (a->m + kBM - 1) / kBM);
-    static bool attr[2] = {false, false};
-    if (dual) {
-        if (!attr[1]) {
-            LLMB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr[1] = true;
-        }
-        gemm_tc_kernel<true><<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
-    } else {
-        if (!attr[0]) {
-            LLMB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr[0] = true;
-        }
-        gemm_tc_kernel<false><<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
+    const dim3 grid(m_tiles, a->n / bn);
+    void (*kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams) =
+        dual ? (bn == 128 ? gemm_tc_kernel<true, 128> : bn == 64 ? gemm_tc_kernel<true, 64> : gemm_tc_kernel<true, 32>)
+             : (bn == 128 ? gemm_tc_kernel<false, 128> : bn == 64 ? gemm_tc_kernel<false, 64> : gemm_tc_kernel<false, 32>);
+    static bool attr_set[2][3] = {};
+    bool &done = attr_set[dual ? 1 : 0][bn == 128 ? 0 : bn == 64 ? 1 : 2];
+    if (!done) {
+        LLMB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        done = true;
     }
+    kernel<<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
     LLMB_CUDA_OK(cudaGetLastError());
     return LLMB_OK;
 }

@@ -5,13 +5,11 @@
 //                  binary reduction tree, eps added in double, IEEE division, FP16 rounding.
 //   attn_prefill   causal attention of M new rows against the KV cache (replaces compute_attention's
 //                  three kernels, inference.cu:698-947): scores (q.k)/sqrtf(head_dim) in FP32 from
-//                  FP16, softmax in FP32 (online, never materialising the N x N matrix), P.V in FP32,
-//                  FP16 out.  K and V come from the cache rows the QKV projection just appended, so a
-//                  chunk that starts at position pos0 > 0 attends to the earlier rows as well.
+//                  FP16, softmax in FP32 (online, never materialising the N x N matrix), P.V with FP32
+//                  accumulation, FP16 out.  K and V come from the cache rows the QKV projection just
+//                  appended, so a chunk that starts at position pos0 > 0 attends to the earlier rows
+//                  as well.
 //   iota           positions pos0 .. pos0 + n - 1 for the embedding / RoPE-angle prologue.
-//
-// attn_prefill runs on the CUDA cores (32 query rows x one head per CTA, 32-row K/V tiles staged in
-// shared memory); it is bound by FP32 FMA issue, not by memory.
 #include "common.cuh"
 #include "gemv_common.cuh"
 
@@ -46,44 +44,81 @@ rmsnorm_rows_kernel(const __half *__restrict__ x, const __half *__restrict__ gam
     for (int c = tid; c < nchunks; c += kNormThreads) yr[c] = rmsnorm_apply8(xr[c], __ldg(gr + c), rms);
 }
 
-constexpr int kPfRows = 32;     // query rows per CTA
-constexpr int kPfTile = 32;     // K/V rows per shared-memory tile
-constexpr int kPfThreads = 128; // 4 threads per query row
+// ---------------------------------------------------------------------------------------------
+// Block attention on the tensor cores (warp-level mma.sync m16n8k16, FP16 in, FP32 accumulate).
+// CTA = 64 query rows of one head, 4 warps x 16 rows; K/V tiles of 64 cache rows in padded shared
+// memory.  Per tile and warp: S = Q K^T (fragments of Q live in registers for the whole kernel),
+// scores / sqrtf(head_dim) and the online softmax in FP32 on the accumulator fragments, then
+// O += P V with P split into an FP16 head and an FP16 remainder (two MMAs), so that the
+// probabilities enter the product with ~22 bits as the reference's FP32 P does, not with 11.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaRows = 64;   // query rows per CTA
+constexpr int kMmaTile = 64;   // cache rows per tile
+constexpr int kMmaThreads = 128;
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
 
 template <int HD>
-__global__ void __launch_bounds__(kPfThreads)
-attn_prefill_kernel(const __half *__restrict__ q, const __half *__restrict__ k_cache, const __half *__restrict__ v_cache,
-                    __half *__restrict__ out, int m, int pos0, int n_q_heads, int n_kv_heads) {
-    constexpr int KP = HD + 8;  // padded K row: the four key rows a quad reads fall in different banks
-    constexpr int DQ = HD / 4;  // output columns per thread
-    __shared__ __align__(16) __half k_s[kPfTile][KP];
-    __shared__ __align__(16) __half v_s[kPfTile][HD];
-    __shared__ float s_s[kPfRows][kPfTile + 1];
+__global__ void __launch_bounds__(kMmaThreads)
+attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__ k_cache,
+                        const __half *__restrict__ v_cache, __half *__restrict__ out, int m, int pos0, int n_q_heads,
+                        int n_kv_heads) {
+    constexpr int KP = HD + 8;     // padded row: 16-byte aligned, and 8 consecutive rows fall in distinct banks
+    constexpr int KS = HD / 16;    // k-steps of Q K^T
+    constexpr int NT = kMmaTile / 8;  // score n-tiles per tile
+    constexpr int OT = HD / 8;     // output n-tiles
+    __shared__ __align__(16) __half k_s[kMmaTile][KP];
+    __shared__ __align__(16) __half v_s[kMmaTile][KP];
 
-    const int tid = threadIdx.x, r = tid >> 2, qd = tid & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
     const int head = blockIdx.y, kvh = head / (n_q_heads / n_kv_heads);
-    const int m0 = blockIdx.x * kPfRows;
-    const int row = min(m0 + r, m - 1);        // tail rows repeat the last row and are not stored
-    const int qpos = pos0 + row;               // keys 0 .. qpos are visible
-    const int last_pos = pos0 + min(m0 + kPfRows, m) - 1;
+    const int m0 = blockIdx.x * kMmaRows;
     const int n_q = n_q_heads * HD, n_kv = n_kv_heads * HD;
-    const float inv_sqrt = sqrtf((float)HD);
+    // this thread's two rows (tail rows repeat the last row and are not stored)
+    const int r0 = m0 + warp * 16 + quad_row, r1 = r0 + 8;
+    const int row0 = min(r0, m - 1), row1 = min(r1, m - 1);
+    const int qpos0 = pos0 + row0, qpos1 = pos0 + row1;
+    const int last_pos = pos0 + min(m0 + kMmaRows, m) - 1;
+    const float sqrt_hd = sqrtf((float)HD);
 
-    __half2 qreg[HD / 2];
+    uint32_t qf[KS][4];
     {
-        const uint4 *qr = reinterpret_cast<const uint4 *>(q + (size_t)row * n_q + (size_t)head * HD);
+        const __half *q0 = q + (size_t)row0 * n_q + (size_t)head * HD + quad_col;
+        const __half *q1 = q + (size_t)row1 * n_q + (size_t)head * HD + quad_col;
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4 *>(qreg)[i] = qr[i];
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = *reinterpret_cast<const uint32_t *>(q0 + ks * 16);
+            qf[ks][1] = *reinterpret_cast<const uint32_t *>(q1 + ks * 16);
+            qf[ks][2] = *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8);
+            qf[ks][3] = *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8);
+        }
     }
-    float acc[DQ];
+    float o[OT][4];
 #pragma unroll
-    for (int i = 0; i < DQ; ++i) acc[i] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
+    for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
+    float m_run0 = -INFINITY, m_run1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // l: this thread's share of the row sum
 
-    for (int kv0 = 0; kv0 <= last_pos; kv0 += kPfTile) {
+    for (int kv0 = 0; kv0 <= last_pos; kv0 += kMmaTile) {
         __syncthreads();  // the previous tile has been consumed
         constexpr int kChunks = HD / 8;
-        for (int i = tid; i < kPfTile * kChunks; i += kPfThreads) {
+        for (int i = tid; i < kMmaTile * kChunks; i += kMmaThreads) {
             const int c = i / kChunks, part = i % kChunks;
             uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
             if (kv0 + c <= last_pos) {  // rows past the last visible key are never read from the cache
@@ -95,61 +130,92 @@ attn_prefill_kernel(const __half *__restrict__ q, const __half *__restrict__ k_c
             *reinterpret_cast<uint4 *>(&v_s[c][part * 8]) = vv;
         }
         __syncthreads();
-        // scores of this row against keys qd, qd + 4, ...
-        float sc[kPfTile / 4];
-        float tile_max = -INFINITY;
+
+        // S = Q K^T: B fragment of n-tile t, k-step ks = K[t * 8 + lane / 4][ks * 16 + 2 (lane % 4) (+ 8)]
+        float sc[NT][4];
 #pragma unroll
-        for (int j = 0; j < kPfTile / 4; ++j) {
-            const int c = qd + 4 * j;
-            const __half2 *kr = reinterpret_cast<const __half2 *>(&k_s[c][0]);
-            float dot = 0.0f;
+        for (int t = 0; t < NT; ++t) {
+            sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.0f;
+            const __half *kr = &k_s[t * 8 + quad_row][quad_col];
 #pragma unroll
-            for (int i = 0; i < HD / 2; ++i) {
-                const float2 a = __half22float2(qreg[i]), b = __half22float2(kr[i]);
-                dot = __fmaf_rn(a.x, b.x, dot);
-                dot = __fmaf_rn(a.y, b.y, dot);
+            for (int ks = 0; ks < KS; ++ks)
+                mma_16816(sc[t], qf[ks], *reinterpret_cast<const uint32_t *>(kr + ks * 16),
+                          *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8));
+        }
+        // scale, causal mask, tile maximum per row
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const int key = kv0 + t * 8 + quad_col;
+            sc[t][0] = key <= qpos0 ? __fdiv_rn(sc[t][0], sqrt_hd) : -INFINITY;
+            sc[t][1] = key + 1 <= qpos0 ? __fdiv_rn(sc[t][1], sqrt_hd) : -INFINITY;
+            sc[t][2] = key <= qpos1 ? __fdiv_rn(sc[t][2], sqrt_hd) : -INFINITY;
+            sc[t][3] = key + 1 <= qpos1 ? __fdiv_rn(sc[t][3], sqrt_hd) : -INFINITY;
+            tmax0 = fmaxf(tmax0, fmaxf(sc[t][0], sc[t][1]));
+            tmax1 = fmaxf(tmax1, fmaxf(sc[t][2], sc[t][3]));
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        // key 0 is visible to every row, so the running maximum is finite from the first tile on
+        const float mn0 = fmaxf(m_run0, tmax0), mn1 = fmaxf(m_run1, tmax1);
+        const float scale0 = expf(m_run0 - mn0), scale1 = expf(m_run1 - mn1);
+        m_run0 = mn0;
+        m_run1 = mn1;
+        l0 *= scale0;
+        l1 *= scale1;
+#pragma unroll
+        for (int t = 0; t < OT; ++t) {
+            o[t][0] *= scale0;
+            o[t][1] *= scale0;
+            o[t][2] *= scale1;
+            o[t][3] *= scale1;
+        }
+        // probabilities as A fragments: two adjacent score n-tiles make one 16-key k-step
+        uint32_t p_hi[NT / 2][4], p_lo[NT / 2][4];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float pr[4];
+            pr[0] = expf(sc[t][0] - mn0);
+            pr[1] = expf(sc[t][1] - mn0);
+            pr[2] = expf(sc[t][2] - mn1);
+            pr[3] = expf(sc[t][3] - mn1);
+            l0 += pr[0] + pr[1];
+            l1 += pr[2] + pr[3];
+            const __half2 h01 = __floats2half2_rn(pr[0], pr[1]), h23 = __floats2half2_rn(pr[2], pr[3]);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const int j = t >> 1, base = (t & 1) * 2;
+            p_hi[j][base] = *reinterpret_cast<const uint32_t *>(&h01);
+            p_hi[j][base + 1] = *reinterpret_cast<const uint32_t *>(&h23);
+            p_lo[j][base] = pack_half2(pr[0] - f01.x, pr[1] - f01.y);
+            p_lo[j][base + 1] = pack_half2(pr[2] - f23.x, pr[3] - f23.y);
+        }
+        // O += P V: B fragments of V through ldmatrix.trans (V rows are keys, the MMA wants keys along k)
+#pragma unroll
+        for (int j = 0; j < NT / 2; ++j) {
+#pragma unroll
+            for (int t2 = 0; t2 < OT / 2; ++t2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3, rr = lane & 7;
+                ldmatrix_x4_trans(vb, &v_s[j * 16 + (mat & 1) * 8 + rr][t2 * 16 + (mat >> 1) * 8]);
+                mma_16816(o[2 * t2], p_hi[j], vb[0], vb[1]);
+                mma_16816(o[2 * t2], p_lo[j], vb[0], vb[1]);
+                mma_16816(o[2 * t2 + 1], p_hi[j], vb[2], vb[3]);
+                mma_16816(o[2 * t2 + 1], p_lo[j], vb[2], vb[3]);
             }
-            sc[j] = (kv0 + c <= qpos) ? __fdiv_rn(dot, inv_sqrt) : -INFINITY;
-            tile_max = fmaxf(tile_max, sc[j]);
         }
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-        const float m_new = fmaxf(m_run, tile_max);  // finite: key kv0 <= qpos is visible in every tile started
-        const float scale = expf(m_run - m_new);     // expf(-inf) = 0 on the first tile
-        float psum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < kPfTile / 4; ++j) {
-            const float pj = expf(sc[j] - m_new);
-            s_s[r][qd + 4 * j] = pj;
-            psum += pj;
-        }
-        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-        l_run = l_run * scale + psum;
-        m_run = m_new;
-        __syncwarp();  // row r of s_s is written and read by the four threads of one quad only
-#pragma unroll
-        for (int i = 0; i < DQ; ++i) acc[i] *= scale;
-#pragma unroll 4
-        for (int c = 0; c < kPfTile; ++c) {
-            const float pc = s_s[r][c];
-            const __half2 *vr = reinterpret_cast<const __half2 *>(&v_s[c][qd * DQ]);
-#pragma unroll
-            for (int i = 0; i < DQ / 2; ++i) {
-                const float2 vv = __half22float2(vr[i]);
-                acc[2 * i] = __fmaf_rn(pc, vv.x, acc[2 * i]);
-                acc[2 * i + 1] = __fmaf_rn(pc, vv.y, acc[2 * i + 1]);
-            }
-        }
-        __syncwarp();
     }
-    if (m0 + r < m) {
-        __align__(16) __half o[DQ];
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __half *o0 = out + (size_t)row0 * n_q + (size_t)head * HD + quad_col;
+    __half *o1 = out + (size_t)row1 * n_q + (size_t)head * HD + quad_col;
 #pragma unroll
-        for (int i = 0; i < DQ; ++i) o[i] = __float2half_rn(__fdiv_rn(acc[i], l_run));
-        uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)row * n_q + (size_t)head * HD + qd * DQ);
-#pragma unroll
-        for (int i = 0; i < DQ / 8; ++i) dst[i] = reinterpret_cast<const uint4 *>(o)[i];
+    for (int t = 0; t < OT; ++t) {
+        if (r0 < m) *reinterpret_cast<uint32_t *>(o0 + t * 8) = pack_half2(__fdiv_rn(o[t][0], l0), __fdiv_rn(o[t][1], l0));
+        if (r1 < m) *reinterpret_cast<uint32_t *>(o1 + t * 8) = pack_half2(__fdiv_rn(o[t][2], l1), __fdiv_rn(o[t][3], l1));
     }
 }
 
@@ -188,13 +254,13 @@ extern "C" int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache,
         n_q_heads % n_kv_heads)
         return LLMB_ERR_INVALID;
     if (n_q_heads > 65535) return LLMB_ERR_UNSUPPORTED;
-    const dim3 grid((m + kPfRows - 1) / kPfRows, n_q_heads);
+    const dim3 grid((m + kMmaRows - 1) / kMmaRows, n_q_heads);
     cudaStream_t s = static_cast<cudaStream_t>(stream_);
     const __half *q = reinterpret_cast<const __half *>(d_q), *kc = reinterpret_cast<const __half *>(d_k_cache),
                  *vc = reinterpret_cast<const __half *>(d_v_cache);
     __half *o = reinterpret_cast<__half *>(d_out);
-    if (head_dim == 128) attn_prefill_kernel<128><<<grid, kPfThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
-    else if (head_dim == 64) attn_prefill_kernel<64><<<grid, kPfThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
+    if (head_dim == 128) attn_prefill_mma_kernel<128><<<grid, kMmaThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
+    else if (head_dim == 64) attn_prefill_mma_kernel<64><<<grid, kMmaThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
     else {
         set_last_error("llmb_attn_prefill: head_dim must be 64 or 128");
         return LLMB_ERR_UNSUPPORTED;

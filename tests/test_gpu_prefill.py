@@ -61,11 +61,12 @@ def test_epilogue_constants_match_header(pkg):
         assert m and int(m.group(1)) == val, name
 
 
+@pytest.mark.parametrize("tile_n", [0, 32, 64, 128])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (16, 256, 256), (200, 384, 768), (300, 512, 4096), (1, 128, 128)])
-def test_gemm_store(pkg, oracle, m, n, k):
+def test_gemm_store(pkg, oracle, m, n, k, tile_n):
     a, b = mats(oracle, m, n, k)
     out = torch.full((m + 3, n), 0x7BFF, dtype=torch.int16, device="cuda")  # rows past m must stay untouched
-    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_STORE)
+    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_STORE, tile_n=tile_n)
     got = host_u16(out)
     want = matmul64(a, b)
     print("gemm %dx%dx%d: max abs err %.3g" % (m, n, k, np.abs(f16(got[:m]) - want).max()))
@@ -73,12 +74,13 @@ def test_gemm_store(pkg, oracle, m, n, k):
     assert (got[m:] == 0x7BFF).all()
 
 
-def test_gemm_residual(pkg, oracle):
+@pytest.mark.parametrize("tile_n", [32, 64, 128])
+def test_gemm_residual(pkg, oracle, tile_n):
     m, n, k = 150, 256, 512
     a, b = mats(oracle, m, n, k, 1)
     res = oracle.synth_fp16(7, 3, m * n, std=1.0).reshape(m, n)
     out = dev(res.copy())
-    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_RESIDUAL)
+    gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_RESIDUAL, tile_n=tile_n)
     acc = matmul64(a, b)
     want = acc.astype(np.float16).astype(np.float64) + f16(res).astype(np.float64)
     # half(acc) may sit one FP16 ulp from the FP64 product's rounding; after the add cancels, that ulp of
@@ -87,18 +89,20 @@ def test_gemm_residual(pkg, oracle):
                       abs_tol=np.abs(acc) * 2.0 ** -10 + tc_tol(acc, k))
 
 
-def test_gemm_swiglu(pkg, oracle):
+@pytest.mark.parametrize("tile_n", [32, 64, 128])
+def test_gemm_swiglu(pkg, oracle, tile_n):
     m, n, k = 130, 384, 256
     a, b = mats(oracle, m, n, k, 2)
     b2 = oracle.synth_fp16(8, 4, n * k, std=0.02).reshape(n, k)
     out = torch.zeros((m, n), dtype=torch.int16, device="cuda")
-    gemm(pkg, a=dev(a), b=dev(b), b2=dev(b2), c=out, m=m, n=n, k=k, epilogue=EPI_SWIGLU)
+    gemm(pkg, a=dev(a), b=dev(b), b2=dev(b2), c=out, m=m, n=n, k=k, epilogue=EPI_SWIGLU, tile_n=tile_n)
     g, u = matmul64(a, b), matmul64(a, b2)
     want = g / (1.0 + np.exp(-g)) * u
     assert_close_fp16(host_u16(out).reshape(m, n), want, what="gemm swiglu", abs_tol=tc_tol(want, k))
 
 
-def test_gemm_rope_kv(pkg, oracle):
+@pytest.mark.parametrize("tile_n", [32, 64, 128])
+def test_gemm_rope_kv(pkg, oracle, tile_n):
     hd, nqh, nkvh, k, m, pos0, max_pos = 64, 4, 2, 256, 70, 5, 128
     n_q, n_kv = nqh * hd, nkvh * hd
     n = n_q + 2 * n_kv
@@ -112,7 +116,7 @@ def test_gemm_rope_kv(pkg, oracle):
     kc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
     vc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
     gemm(pkg, a=dev(a), b=dev(b), c=q_out, m=m, n=n, k=k, epilogue=EPI_ROPE_KV, n_q=n_q, n_kv=n_kv, head_dim=hd,
-         rope_cs=dev(cs), k_cache=kc, v_cache=vc, pos0=pos0, max_pos=max_pos)
+         rope_cs=dev(cs), k_cache=kc, v_cache=vc, pos0=pos0, max_pos=max_pos, tile_n=tile_n)
     y = matmul64(a, b).astype(np.float16).astype(np.float64)
 
     def rope(block, heads):
@@ -145,6 +149,8 @@ def test_gemm_rejects_unaligned_shapes(pkg):
     assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
     a = pkg.GemmArgs(a=t.data_ptr(), b=t.data_ptr(), c=t.data_ptr(), m=0, n=128, k=64, epilogue=EPI_STORE)
     assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
+    a = pkg.GemmArgs(a=t.data_ptr(), b=t.data_ptr(), c=t.data_ptr(), m=4, n=128, k=64, epilogue=EPI_STORE, tile_n=48)
+    assert pkg.lib.llmb_gemm_f16(C.byref(a), None) != 0
 
 
 @pytest.mark.parametrize("m,d", [(5, 256), (33, 4096), (3, 1000)])
@@ -161,7 +167,7 @@ def test_rmsnorm_rows_bit_exact(pkg, oracle, m, d):
         assert_close_fp16(got[r], f16(want).astype(np.float64), what="rmsnorm row %d" % r)
 
 
-@pytest.mark.parametrize("hd,nqh,nkvh,m,pos0", [(64, 4, 2, 45, 0), (128, 8, 2, 70, 37), (128, 4, 4, 1, 3)])
+@pytest.mark.parametrize("hd,nqh,nkvh,m,pos0", [(64, 4, 2, 45, 0), (128, 8, 2, 70, 37), (128, 4, 4, 1, 3), (128, 4, 1, 200, 100), (64, 2, 2, 130, 0)])
 def test_attn_prefill_matches_fp64(pkg, oracle, hd, nqh, nkvh, m, pos0):
     total = pos0 + m
     n_q, n_kv = nqh * hd, nkvh * hd
