@@ -112,6 +112,7 @@ __device__ __forceinline__ int rows_per_stage(int k) {
 
 // Projection number `ph` of the step: 4 * layer + {QKV, O, GU, DOWN}, then the lm_head.
 // `emb` is the embedding row of this step's token.
+template <bool kTp>
 __device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, const DsLayer *layers, int ph, const __half *emb) {
     GemvDesc g;
     const int l = ph >> 2;
@@ -142,7 +143,7 @@ __device__ __forceinline__ GemvDesc gemv_desc(const DsParams &p, const DsLayer *
             if (p.hidden) g.hidden_row = p.hidden + (size_t)(l + 1) * p.d;
         }
     }
-    if (p.tp_size > 1) {
+    if (kTp) {
         // all-reduce 2l follows o_proj of layer l, 2l + 1 follows its down_proj; the reduced row lands
         // in residual buffer (number & 1), the previous row is in the other one (or the embedding)
         __half *xb[2] = {p.x, p.x_alt};
@@ -211,12 +212,13 @@ struct DsCursor {
 };
 
 // Requests the next ring stage, walking on through the projections in program order.
+template <bool kTp>
 __device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv,
                                                  unsigned char *ring, uint64_t *full_bar, uint64_t policy) {
     while (c.rg >= c.rg_end) {
         if (c.ph + 1 >= n_gemv) { c.ph = n_gemv; return; }
         ++c.ph;
-        const GemvDesc g = gemv_desc(p, layers, c.ph, emb);
+        const GemvDesc g = gemv_desc<kTp>(p, layers, c.ph, emb);
         c.w = reinterpret_cast<const unsigned char *>(g.w);
         c.w2 = reinterpret_cast<const unsigned char *>(g.w2);
         c.row_bytes = (size_t)g.k * 2;
@@ -255,6 +257,8 @@ __device__ __forceinline__ float stage_dot(const unsigned char *base, size_t row
     return warp_reduce_multi<NR>(acc, lane);
 }
 
+// kTp = false compiles every tensor-parallel branch out of the single-GPU kernel.
+template <bool kTp>
 __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsParams p) {
     extern __shared__ __align__(128) unsigned char ds_smem[];
     unsigned char *ring = ds_smem;
@@ -292,14 +296,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
 
     // End of a phase for this CTA: all its global writes are ordered before the arrival.
     // the cross-GPU synchronisation number lives in this rank's exchange block (never reset locally)
-    unsigned long long *tp_state = p.tp_size > 1 ? reinterpret_cast<unsigned long long *>(p.peer[p.tp_rank] + 128) : nullptr;
+    unsigned long long *tp_state = kTp ? reinterpret_cast<unsigned long long *>(p.peer[p.tp_rank] + 128) : nullptr;
     const unsigned long long tp_base = tp_state ? tp_state[0] : 0ULL;
     const unsigned int tag_base = tp_state ? (unsigned int)tp_state[1] : 0u;  // all-reduces done before this launch
     unsigned long long n_tp = 0;   // cross-GPU synchronisations passed in this launch
     auto grid_arrive = [&]() {
         named_bar_sync(3, kDsThreads);
         if (tid == 0) {
-            if (p.tp_size > 1) __threadfence_system();  // partial sums were stored into the peers' memory
+            if (kTp) __threadfence_system();  // partial sums were stored into the peers' memory
             else __threadfence();
             atomicAdd(p.bar, 1ULL);
         }
@@ -325,7 +329,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         const int kind = (prev_ph < 4 * p.n_layers) ? (prev_ph & 3) : PH_LM;
         // tensor parallel: the partial sums of o_proj / down_proj carry their own tags, so the next
         // phase needs no grid-wide wait at all; the arrival is still counted
-        if (p.tp_size > 1 && (kind == PH_O || kind == PH_DOWN)) ++n_bar;
+        if (kTp && (kind == PH_O || kind == PH_DOWN)) ++n_bar;
         else grid_wait();
     };
 
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         cur.row_bytes = 0;
         cur.n = cur.R = 0;
         if (lane == 0)
-            for (int k = 0; k < kDsSlots; ++k) issue_next_stage(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+            for (int k = 0; k < kDsSlots; ++k) issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
         float best_val = -INFINITY;
         int best_idx = 0x7fffffff;
         uint32_t it = 0;
@@ -352,14 +356,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             }
         };
         for (int ph = 0; ph < n_gemv; ++ph) {
-            const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
+            const GemvDesc g = gemv_desc<kTp>(p, layer_s, ph, emb);
             if (ph > 0) wait_after(ph - 1);
             fstamp(ph, 4);
             int gb, ge;
             cta_range((g.n + g.R - 1) / g.R, gb, ge);
             const unsigned mask = (1u << g.nr) - 1u;
             // Residual rows of this CTA: one batch of L2 loads per phase, not one round trip per stage.
-            const int res_rows = (g.res && g.scatter < 0) ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
+            const int res_rows = (g.res && !(kTp && g.scatter >= 0)) ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
             const bool res_cached = res_rows <= 128;
             if (res_cached) {
                 for (int i = lane; i < res_rows; i += 32) sh.res_s[i] = __half2float(__ldcg(&g.res[gb * g.R + i]));
@@ -397,7 +401,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                         }
                         idx += p.vocab_offset;  // tensor parallel: this rank holds a slice of the vocabulary
                         if (v > best_val || (v == best_val && idx < best_idx)) { best_val = v; best_idx = idx; }
-                    } else if (g.scatter >= 0) {
+                    } else if (kTp && g.scatter >= 0) {
                         // tensor parallel: this rank's partial sum goes to every rank's receive buffer
                         if (lane < rows) {
                             const size_t off = kTpRecvOff + (((size_t)(g.scatter & 1) * p.tp_size + p.tp_rank) * p.d + row0 + lane) * 8;
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 }
                 __syncwarp();
                 // slot s is free (all 8 warps have read it) and its partials are consumed: refill
-                if (lane == 0 && got) issue_next_stage(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+                if (lane == 0 && got) issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
             }
             // Stores into the peers' memory are posted over NVLink: the warp that issued them waits for
             // them itself, a fence by another thread after a CTA barrier does not cover them.
@@ -477,7 +481,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     uint32_t it = 0;
 
     for (int ph = 0; ph < n_gemv; ++ph) {
-        const GemvDesc g = gemv_desc(p, layer_s, ph, emb);
+        const GemvDesc g = gemv_desc<kTp>(p, layer_s, ph, emb);
         const int nchunks = g.k >> 3;
         const size_t row_bytes = (size_t)g.k * 2;
         bool have[kDsJ];
@@ -498,7 +502,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         constexpr int kNormJ = kDsJ / 2;  // normalised inputs have k = d_model <= 8192
         uint4 xh[kDsJ];
         uint4 gv[kNormJ];
-        if (g.reduce < 0) {
+        if (!kTp || g.reduce < 0) {
 #pragma unroll
             for (int j = 0; j < kDsJ; ++j)
                 xh[j] = have[j] ? __ldcg(reinterpret_cast<const uint4 *>(g.x) + gtid + kDsGThreads * j) : make_uint4(0, 0, 0, 0);
@@ -826,7 +830,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     // rank could start the next step and overwrite receive buffer 0 while a slow rank still reads it.
     // Waiting here for every rank's last partial sums keeps the ranks within one all-reduce of each
     // other, which is what the double buffering relies on.
-    if (p.tp_size > 1 && !p.with_logits) {
+    if (kTp && !p.with_logits) {
         const int last = 2 * p.n_layers - 1;
         const unsigned char *recv = p.peer[p.tp_rank] + kTpRecvOff + (size_t)(last & 1) * p.tp_size * p.d * 8;
         const unsigned int tag = tag_base + (unsigned int)last + 1u;
@@ -867,7 +871,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 const int oi = __shfl_xor_sync(0xffffffffu, idx, m);
                 if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
             }
-            if (p.tp_size > 1) {
+            if (kTp) {
                 // each rank's best logit goes to every rank; then one more announcement round
                 if (lane == 0) {
                     for (int r = 0; r < p.tp_size; ++r) {
@@ -913,7 +917,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             }
             *p.pos = np;
             p.bar[1] = bar_base + n_bar * (unsigned long long)gridDim.x;
-            if (tp_state) {
+            if (kTp) {
                 tp_state[0] = tp_base + n_tp;
                 tp_state[1] = (unsigned long long)(tag_base + 2u * (unsigned int)p.n_layers);
             }
@@ -1024,13 +1028,14 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
     if (!smem_limit) {
         cudaFuncAttributes fa;
         int optin = 0;
-        LLMB_CUDA_OK(cudaFuncGetAttributes(&fa, decode_step_kernel));
+        LLMB_CUDA_OK(cudaFuncGetAttributes(&fa, decode_step_kernel<true>));
         LLMB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         smem_limit = (size_t)optin > fa.sharedSizeBytes ? (size_t)optin - fa.sharedSizeBytes : 0;
     }
     if (smem > smem_limit) return LLMB_ERR_UNSUPPORTED;  // too many layers for the shared-memory table
     if (smem > smem_set) {
-        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
     cudaLaunchConfig_t cfg = {};
@@ -1043,6 +1048,7 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    LLMB_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_step_kernel, p));
+    if (p.tp_size > 1) LLMB_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_step_kernel<true>, p));
+    else LLMB_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_step_kernel<false>, p));
     return LLMB_OK;
 }

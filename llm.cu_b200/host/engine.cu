@@ -68,7 +68,7 @@ struct Engine {
     bool tp_connected = false;
     unsigned long long *trace = nullptr;  // optional per-phase timestamps of the step kernel
     size_t trace_bytes = 0;
-    int *h_next = nullptr;  // pinned
+    int *h_next = nullptr;  // pinned: [0] next token, [1] device status word
     __half *hidden = nullptr;
     bool use_graph = true, use_pdl = true, copy_logits = true, hidden_dump = false;
     bool greedy_state = false;  // device history[consumed.size()] holds a sampled token not yet fed
@@ -416,14 +416,19 @@ int feed_tokens(Engine *e, const int *ids, int from, int to) {
     return LLMB_OK;
 }
 
-// After a synchronisation point: has any bounded device-side wait given up?  The status word stays
-// set (the kernels then skip their waits) until the caller reads it with llmb_device_status().
-int check_device_status(Engine *e) {
-    int st = 0;
+// Has any bounded device-side wait given up?  The status word is copied to pinned memory on the
+// engine's stream before a synchronisation the caller makes anyway (queue_status_read), and looked
+// at after it (status_result): no extra round trip.  The word stays set (the kernels then skip their
+// waits) until the caller reads it with llmb_device_status().
+int queue_status_read(Engine *e) {
     int *p = device_status_ptr();
     if (!p) return LLMB_ERR_CUDA;
-    LLMB_CUDA_OK(cudaMemcpyAsync(&st, p, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
-    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    LLMB_CUDA_OK(cudaMemcpyAsync(e->h_next + 1, p, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return LLMB_OK;
+}
+
+int status_result(Engine *e) {
+    const int st = e->h_next[1];
     if (st != 0) {
         char msg[160];
         snprintf(msg, sizeof msg, "a bounded device-side wait gave up (status %d)%s", st,
@@ -792,9 +797,10 @@ extern "C" int inference(Llama3 *m, Tensor *X, int *d_tokens, int *h_tokens, Cud
     if (e->copy_logits)
         cudaMemcpyAsync(cache->h_token_probdist, e->logits, (size_t)e->vocab * 2, cudaMemcpyDeviceToHost, e->stream);
     cudaMemcpyAsync(e->h_next, e->d_next, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+    if ((rc = queue_status_read(e))) return -rc;
     cudaError_t ce = cudaStreamSynchronize(e->stream);
     if (ce != cudaSuccess) return -cuda_fail(ce, __FILE__, __LINE__);
-    if ((rc = check_device_status(e))) return -rc;
+    if ((rc = status_result(e))) return -rc;
     e->consumed.assign(ids, ids + count);
     e->greedy_state = true;  // the argmax kernel appended the sampled token to the device history
     return e->h_next[0];
@@ -818,8 +824,9 @@ extern "C" int inference_greedy(Llama3 *m, CudaCache *cache, const int *prompt, 
     LLMB_CUDA_OK(cudaEventRecord(e->ev[2], e->stream));
     LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + n_prompt, sizeof(int) * (size_t)n_new,
                                  cudaMemcpyDeviceToHost, e->stream));
+    if ((rc = queue_status_read(e))) return rc;
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
-    if ((rc = check_device_status(e))) return rc;
+    if ((rc = status_result(e))) return rc;
     if (prefill_ms) LLMB_CUDA_OK(cudaEventElapsedTime(prefill_ms, e->ev[0], e->ev[1]));
     if (decode_ms) LLMB_CUDA_OK(cudaEventElapsedTime(decode_ms, e->ev[1], e->ev[2]));
     // the cache now holds prompt + all but the last generated token
@@ -851,8 +858,9 @@ extern "C" int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int 
                                  e->stream));
     LLMB_CUDA_OK(cudaMemcpyAsync(out_tokens, e->d_history + P + 1, sizeof(int) * (size_t)n_steps,
                                  cudaMemcpyDeviceToHost, e->stream));
+    if ((rc = queue_status_read(e))) return rc;
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
-    if ((rc = check_device_status(e))) return rc;
+    if ((rc = status_result(e))) return rc;
     if (ms) LLMB_CUDA_OK(cudaEventElapsedTime(ms, e->ev[0], e->ev[1]));
     e->consumed.insert(e->consumed.end(), fed.begin(), fed.end());
     return LLMB_OK;
