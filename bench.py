@@ -152,6 +152,7 @@ def run_ours(args):
     # ---- end to end through inference(): host tokens in, token + logits out ---------------
     cache.reset()
     seq = list(prompt)
+    barrier()                                     # tensor-parallel ranks must enter a step together
     seq.append(cache.infer(seq))                  # prefill (untimed)
     for _ in range(max(W, 3)):
         seq.append(cache.infer(seq))

@@ -49,7 +49,7 @@ constexpr uint32_t kDsSlotBytes = 32 * 1024;
 constexpr int kDsJ = 8;                           // 16-byte chunks of x per thread: k <= 16384
 constexpr int kDsTile = 32;                       // cache rows per attention tile
 constexpr uint32_t kPollLimit = 1u << 22;
-constexpr uint32_t kTagPollLimit = 1u << 18;  // tagged peer data: about half a second
+constexpr uint32_t kTagPollLimit = 1u << 20;  // tagged peer data: on the order of a second
 
 struct DsLayer {
     const __half *wqkv, *wo, *wgate, *wup, *wdown, *g_in, *g_post;
