@@ -47,7 +47,7 @@ rmsnorm_rows_kernel(const __half *__restrict__ x, const __half *__restrict__ gam
 // ---------------------------------------------------------------------------------------------
 // Block attention on the tensor cores (warp-level mma.sync m16n8k16, FP16 in, FP32 accumulate).
 // CTA = 64 query rows of one head, 4 warps x 16 rows; K/V tiles of 64 cache rows in padded shared
-// memory.  Per tile and warp: S = Q K^T (fragments of Q live in registers for the whole kernel),
+// memory, double-buffered with cp.async.  Per tile and warp: S = Q K^T (fragments of Q live in registers for the whole kernel),
 // scores / sqrtf(head_dim) and the online softmax in FP32 on the accumulator fragments, then
 // O += P V with P split into an FP16 head and an FP16 remainder (two MMAs), so that the
 // probabilities enter the product with ~22 bits as the reference's FP32 P does, not with 11.
@@ -83,8 +83,11 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
     constexpr int KS = HD / 16;    // k-steps of Q K^T
     constexpr int NT = kMmaTile / 8;  // score n-tiles per tile
     constexpr int OT = HD / 8;     // output n-tiles
-    __shared__ __align__(16) __half k_s[kMmaTile][KP];
-    __shared__ __align__(16) __half v_s[kMmaTile][KP];
+    // two K/V tile buffers in dynamic shared memory: tile t + 1 streams in (cp.async) while tile t is
+    // multiplied
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    typedef __half (*TilePtr)[KP];
+    constexpr size_t kTileBytes = (size_t)kMmaTile * KP * sizeof(__half);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
@@ -115,21 +118,40 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
     for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
     float m_run0 = -INFINITY, m_run1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // l: this thread's share of the row sum
 
-    for (int kv0 = 0; kv0 <= last_pos; kv0 += kMmaTile) {
-        __syncthreads();  // the previous tile has been consumed
+    // Requests tile `t` (cache rows t * 64 ..) into buffer t & 1.  Rows past the last visible key are
+    // never read from the cache: their 16-byte pieces are zero-filled (source size 0).
+    auto request_tile = [&](int t) {
         constexpr int kChunks = HD / 8;
+        TilePtr kd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(t & 1) * 2 * kTileBytes);
+        TilePtr vd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(t & 1) * 2 * kTileBytes + kTileBytes);
+        const int kv0 = t * kMmaTile;
         for (int i = tid; i < kMmaTile * kChunks; i += kMmaThreads) {
             const int c = i / kChunks, part = i % kChunks;
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-            if (kv0 + c <= last_pos) {  // rows past the last visible key are never read from the cache
-                const size_t off = (size_t)(kv0 + c) * n_kv + (size_t)kvh * HD;
-                kv = reinterpret_cast<const uint4 *>(k_cache + off)[part];
-                vv = reinterpret_cast<const uint4 *>(v_cache + off)[part];
-            }
-            *reinterpret_cast<uint4 *>(&k_s[c][part * 8]) = kv;
-            *reinterpret_cast<uint4 *>(&v_s[c][part * 8]) = vv;
+            const bool valid = kv0 + c <= last_pos;
+            const size_t off = (size_t)(valid ? kv0 + c : 0) * n_kv + (size_t)kvh * HD + part * 8;
+            const uint32_t bytes = valid ? 16u : 0u;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&kd[c][part * 8])),
+                         "l"(k_cache + off), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&vd[c][part * 8])),
+                         "l"(v_cache + off), "r"(bytes)
+                         : "memory");
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = last_pos / kMmaTile + 1;
+    request_tile(0);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const int kv0 = tile * kMmaTile;
+        if (tile + 1 < n_tiles) {
+            request_tile(tile + 1);  // its buffer was released by the barrier that ended the previous iteration
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // every thread's pieces of this tile have landed
+        TilePtr k_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(tile & 1) * 2 * kTileBytes);
+        TilePtr v_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(tile & 1) * 2 * kTileBytes + kTileBytes);
 
         // S = Q K^T: B fragment of n-tile t, k-step ks = K[t * 8 + lane / 4][ks * 16 + 2 (lane % 4) (+ 8)]
         float sc[NT][4];
@@ -205,6 +227,7 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
                 mma_16816(o[2 * t2 + 1], p_lo[j], vb[2], vb[3]);
             }
         }
+        __syncthreads();  // this tile has been consumed: its buffer may be refilled
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -259,11 +282,25 @@ extern "C" int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache,
     const __half *q = reinterpret_cast<const __half *>(d_q), *kc = reinterpret_cast<const __half *>(d_k_cache),
                  *vc = reinterpret_cast<const __half *>(d_v_cache);
     __half *o = reinterpret_cast<__half *>(d_out);
-    if (head_dim == 128) attn_prefill_mma_kernel<128><<<grid, kMmaThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
-    else if (head_dim == 64) attn_prefill_mma_kernel<64><<<grid, kMmaThreads, 0, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
-    else {
+    if (head_dim != 64 && head_dim != 128) {
         set_last_error("llmb_attn_prefill: head_dim must be 64 or 128");
         return LLMB_ERR_UNSUPPORTED;
+    }
+    // two buffers x (K tile + V tile) of 64 padded rows
+    const size_t smem = (size_t)4 * kMmaTile * (head_dim + 8) * sizeof(__half);
+    static bool attr_set[2] = {false, false};
+    if (head_dim == 128) {
+        if (!attr_set[0]) {
+            LLMB_CUDA_OK(cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[0] = true;
+        }
+        attn_prefill_mma_kernel<128><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
+    } else {
+        if (!attr_set[1]) {
+            LLMB_CUDA_OK(cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[1] = true;
+        }
+        attn_prefill_mma_kernel<64><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
     }
     LLMB_CUDA_OK(cudaGetLastError());
     return LLMB_OK;
