@@ -10,8 +10,9 @@
 //   tile     128 x BN output per CTA (BN = 128, 64 or 32: the widest that still gives every SM a CTA),
 //            K in steps of 64 (one 128-byte swizzle span of FP16); two CTAs share an SM, so one's
 //            epilogue overlaps the other's main loop
-//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast) fills a 3-stage
-//            (SwiGLU: 2-stage) shared-memory ring, completion on mbarriers
+//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast) fills a shared-memory
+//            ring, completion on mbarriers; 3 stages (SwiGLU: 2) when CTAs share an SM, up to 8 when
+//            the grid is a single partial wave and only the ring can hide the copy latency
 //   warp 1   allocates tensor memory and issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16)
 //            from one elected lane; tcgen05.commit releases ring stages and signals the epilogue
 //   warps 2-5 epilogue: tcgen05.ld the FP32 accumulators (one output row per thread), apply
@@ -28,6 +29,10 @@ namespace llmb {
 constexpr int kBM = 128, kBK = 64;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 16 KB: the A tile of a stage
+constexpr int kGemmMaxStages = 8;
+// Ring depth: two CTAs share an SM when the grid has more CTAs than SMs (3 stages each, 2 for SwiGLU);
+// a grid that leaves every CTA alone on its SM gets a ring as deep as shared memory allows, because
+// then the copy latency is hidden by nothing but the ring.
 __host__ __device__ constexpr int gemm_stages(bool dual) { return dual ? 2 : 3; }
 __host__ __device__ constexpr uint32_t gemm_stage_bytes(bool dual, int bn) { return kATileBytes + (dual ? 2 : 1) * bn * kBK * 2; }
 
@@ -38,6 +43,7 @@ struct GemmParams {
     int *status;
     int M, N, K, epilogue;
     int n_q, n_kv, head_dim, pos0, max_pos;
+    int stages;  // ring depth of this launch (<= kGemmMaxStages)
 };
 
 __device__ __forceinline__ uint64_t umma_desc(const void *smem_tile) {
@@ -87,13 +93,13 @@ __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
     extern __shared__ __align__(1024) unsigned char gemm_smem[];
-    __shared__ __align__(8) uint64_t full_bar[gemm_stages(DUAL)];
-    __shared__ __align__(8) uint64_t empty_bar[gemm_stages(DUAL)];
+    __shared__ __align__(8) uint64_t full_bar[kGemmMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kGemmMaxStages];
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int prior_status;
 
-    constexpr int kGemmStages = gemm_stages(DUAL);
+    const int kGemmStages = p.stages;
     constexpr uint32_t kBTileBytes = kBN * kBK * 2;
     constexpr uint32_t kStageBytes = gemm_stage_bytes(DUAL, kBN);  // every tile a multiple of 1024 bytes
     constexpr uint32_t kTmemCols = (DUAL ? 2 : 1) * kBN < 32 ? 32 : (DUAL ? 2 : 1) * kBN;
@@ -322,17 +328,22 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     if (!p.status) return LLMB_ERR_CUDA;
     p.M = a->m; p.N = a->n; p.K = a->k; p.epilogue = a->epilogue;
     p.n_q = a->n_q; p.n_kv = a->n_kv; p.head_dim = a->head_dim; p.pos0 = a->pos0; p.max_pos = a->max_pos;
-    const size_t smem = (size_t)gemm_stages(dual) * gemm_stage_bytes(dual, bn) + 1024;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const dim3 grid(m_tiles, a->n / bn);
+    p.stages = gemm_stages(dual);
+    if ((int)(grid.x * grid.y) <= sm_count_cached()) {
+        p.stages = (int)((size_t)200 * 1024 / gemm_stage_bytes(dual, bn));
+        if (p.stages > kGemmMaxStages) p.stages = kGemmMaxStages;
+    }
+    const size_t smem = (size_t)p.stages * gemm_stage_bytes(dual, bn) + 1024;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     void (*kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams) =
         dual ? (bn == 128 ? gemm_tc_kernel<true, 128> : bn == 64 ? gemm_tc_kernel<true, 64> : gemm_tc_kernel<true, 32>)
              : (bn == 128 ? gemm_tc_kernel<false, 128> : bn == 64 ? gemm_tc_kernel<false, 64> : gemm_tc_kernel<false, 32>);
-    static bool attr_set[2][3] = {};
-    bool &done = attr_set[dual ? 1 : 0][bn == 128 ? 0 : bn == 64 ? 1 : 2];
-    if (!done) {
+    static size_t attr_set[2][3] = {};
+    size_t &have = attr_set[dual ? 1 : 0][bn == 128 ? 0 : bn == 64 ? 1 : 2];
+    if (smem > have) {
         LLMB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        done = true;
+        have = smem;
     }
     kernel<<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
     LLMB_CUDA_OK(cudaGetLastError());
