@@ -197,6 +197,10 @@ typedef struct {
     int pos0;              /* cache row of A's row 0 */
     int max_pos;
     int tile_n;            /* output columns per CTA: 0 = the widest of 128/64/32 that fills the SMs */
+    void *workspace;       /* optional, 16-byte aligned, its first 4096 bytes zero before the first use (the  */
+    size_t workspace_bytes;/* kernel leaves them zero): lets a launch with few output tiles split K across     */
+                           /* CTAs; partial sums are added in slice order.  One launch at a time per workspace; */
+                           /* 4096 + SMs * 131072 bytes always suffice.                                        */
 } LlmbGemmArgs;
 
 int llmb_gemm_f16(const LlmbGemmArgs *args, llmb_stream_t stream);

@@ -99,7 +99,7 @@ class GemmArgs(C.Structure):
         ("a", C.c_void_p), ("b", C.c_void_p), ("b2", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int), ("n", C.c_int),
         ("k", C.c_int), ("epilogue", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
         ("rope_cs", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("pos0", C.c_int),
-        ("max_pos", C.c_int), ("tile_n", C.c_int),
+        ("max_pos", C.c_int), ("tile_n", C.c_int), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 

@@ -44,6 +44,11 @@ struct GemmParams {
     int M, N, K, epilogue;
     int n_q, n_kv, head_dim, pos0, max_pos;
     int stages;  // ring depth of this launch (<= kGemmMaxStages)
+    // split-K: blockIdx.z takes a slice of K, partial accumulators meet in the workspace and the last
+    // CTA of a tile to arrive adds them in slice order and runs the epilogue
+    int splits;
+    float *ws_part;  // [tiles][splits][128][accumulator columns]
+    int *ws_count;   // [tiles], zero between launches
 };
 
 __device__ __forceinline__ uint64_t umma_desc(const void *smem_tile) {
@@ -98,6 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int prior_status;
+    __shared__ int split_last;
 
     const int kGemmStages = p.stages;
     constexpr uint32_t kBTileBytes = kBN * kBK * 2;
@@ -113,6 +119,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // comes from DRAM once
     const int m0 = blockIdx.x * kBM, n0 = blockIdx.y * kBN;
     const int k_tiles = p.K / kBK;
+    const int kt_begin = (int)((long long)blockIdx.z * k_tiles / p.splits);
+    const int kt_end = (int)((long long)(blockIdx.z + 1) * k_tiles / p.splits);
 
     // a wait that gave up earlier (here or in another kernel) leaves the status word set: do not queue
     // up more bounded waits behind it
@@ -139,9 +147,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
-            for (int kt = 0; kt < k_tiles && ok; ++kt) {
-                const int s = kt % kGemmStages;
-                if (kt >= kGemmStages) ok = mbar_wait(&empty_bar[s], ((kt / kGemmStages) - 1) & 1, p.status, 301);
+            for (int kt = kt_begin, i = 0; kt < kt_end && ok; ++kt, ++i) {
+                const int s = i % kGemmStages;
+                if (i >= kGemmStages) ok = mbar_wait(&empty_bar[s], ((i / kGemmStages) - 1) & 1, p.status, 301);
                 if (!ok) break;
                 unsigned char *st = ring + (size_t)s * kStageBytes;
                 mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
@@ -153,9 +161,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = true;
-            for (int kt = 0; kt < k_tiles && ok; ++kt) {
-                const int s = kt % kGemmStages;
-                ok = mbar_wait(&full_bar[s], (kt / kGemmStages) & 1, p.status, 302);
+            for (int kt = kt_begin, i = 0; kt < kt_end && ok; ++kt, ++i) {
+                const int s = i % kGemmStages;
+                ok = mbar_wait(&full_bar[s], (i / kGemmStages) & 1, p.status, 302);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned char *st = ring + (size_t)s * kStageBytes;
@@ -163,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint64_t b2desc = DUAL ? umma_desc(st + kATileBytes + kBTileBytes) : 0;
 #pragma unroll
                 for (int k = 0; k < kBK / 16; ++k) {
-                    const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
                     // 16 FP16 along K = 32 bytes = 2 descriptor address units inside the swizzle span
                     umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
                     if (DUAL) umma_f16(tmem_base + kBN, adesc + 2 * k, b2desc + 2 * k, kIdesc, acc);
@@ -179,12 +187,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int lane_group = (warp & 3) * 32;
         const int row = m0 + lane_group + lane;
         const bool row_ok = ok && row < p.M;
+        constexpr int kAccCols = (DUAL ? 2 : 1) * kBN;
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        bool finish = true;  // this CTA runs the epilogue
+        if (p.splits > 1) {
+            float *mine = p.ws_part + (((size_t)tile_id * p.splits + blockIdx.z) * kBM + lane_group + lane) * kAccCols;
 #pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16) + (uint32_t)(c * 32);
+                tmem_ld32(taddr, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    reinterpret_cast<uint4 *>(mine + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (DUAL) {
+                    tmem_ld32(taddr + kBN, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        reinterpret_cast<uint4 *>(mine + kBN + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+            }
+            __threadfence();  // this thread's partials are visible device-wide before the arrival is counted
+            named_bar_sync(1, 128);
+            if (threadIdx.x == 64) {
+                const int arrived = atomicAdd(p.ws_count + tile_id, 1);
+                split_last = (arrived == p.splits - 1) ? 1 : 0;
+                if (split_last) p.ws_count[tile_id] = 0;  // ready for the next launch
+                __threadfence();
+            }
+            named_bar_sync(1, 128);
+            finish = split_last != 0;
+        }
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32 && finish; ++c) {
             uint32_t v[32], u[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16) + (uint32_t)(c * 32);
-            tmem_ld32(taddr, v);
-            if (DUAL) tmem_ld32(taddr + kBN, u);
+            if (p.splits > 1) {
+                // partial sums in slice order: the result does not depend on which CTA arrived last
+                float fv[32], fu[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) fv[i] = fu[i] = 0.0f;
+                for (int z = 0; z < p.splits; ++z) {
+                    const float *part = p.ws_part + (((size_t)tile_id * p.splits + z) * kBM + lane_group + lane) * kAccCols + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 t = __ldcg(reinterpret_cast<const float4 *>(part) + i);
+                        fv[4 * i] += t.x; fv[4 * i + 1] += t.y; fv[4 * i + 2] += t.z; fv[4 * i + 3] += t.w;
+                    }
+                    if (DUAL) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 t = __ldcg(reinterpret_cast<const float4 *>(part + kBN) + i);
+                            fu[4 * i] += t.x; fu[4 * i + 1] += t.y; fu[4 * i + 2] += t.z; fu[4 * i + 3] += t.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    v[i] = __float_as_uint(fv[i]);
+                    u[i] = __float_as_uint(fu[i]);
+                }
+            } else {
+                const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16) + (uint32_t)(c * 32);
+                tmem_ld32(taddr, v);
+                if (DUAL) tmem_ld32(taddr + kBN, u);
+            }
             if (!row_ok) continue;
             const int col0 = n0 + c * 32;
             __align__(16) __half out[32];
@@ -303,12 +369,17 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     } else if (a->epilogue != LLMB_EPI_STORE && a->epilogue != LLMB_EPI_RESIDUAL && !dual) {
         return LLMB_ERR_INVALID;
     }
-    // the widest tile that still gives every SM a CTA
+    // Small grids: with a workspace, 128-wide tiles and K split across CTAs until the SMs are covered
+    // (every CTA then streams its own weights and only its slice of the activations); without one, the
+    // widest tile that still gives every SM a CTA.
     const int m_tiles = (a->m + kBM - 1) / kBM;
+    const int sms = sm_count_cached();
+    const bool have_ws = a->workspace && a->workspace_bytes > 4096 && (((uintptr_t)a->workspace) & 15) == 0;
     int bn = a->tile_n;
     if (bn == 0) {
         bn = 128;
-        while (bn > 32 && (a->n / bn) * m_tiles < sm_count_cached()) bn >>= 1;
+        if (!have_ws)
+            while (bn > 32 && (a->n / bn) * m_tiles < sms) bn >>= 1;
     }
     if (bn != 128 && bn != 64 && bn != 32) {
         set_last_error("llmb_gemm_f16: tile_n must be 0, 32, 64 or 128");
@@ -328,9 +399,21 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     if (!p.status) return LLMB_ERR_CUDA;
     p.M = a->m; p.N = a->n; p.K = a->k; p.epilogue = a->epilogue;
     p.n_q = a->n_q; p.n_kv = a->n_kv; p.head_dim = a->head_dim; p.pos0 = a->pos0; p.max_pos = a->max_pos;
-    const dim3 grid(m_tiles, a->n / bn);
+    dim3 grid(m_tiles, a->n / bn);
+    const int tiles = (int)(grid.x * grid.y), k_tiles = a->k / kBK;
+    p.splits = 1;
+    if (have_ws && tiles * 2 <= sms && tiles <= 1024) {
+        int splits = sms / tiles;
+        if (splits > 8) splits = 8;
+        if (splits > k_tiles / 8) splits = k_tiles / 8;
+        const size_t need = 4096 + (size_t)tiles * splits * kBM * (dual ? 2 : 1) * bn * sizeof(float);
+        if (splits > 1 && need <= a->workspace_bytes) p.splits = splits;
+    }
+    p.ws_count = static_cast<int *>(a->workspace);
+    p.ws_part = reinterpret_cast<float *>(static_cast<unsigned char *>(a->workspace) + 4096);
+    grid.z = p.splits;
     p.stages = gemm_stages(dual);
-    if ((int)(grid.x * grid.y) <= sm_count_cached()) {
+    if (tiles * p.splits <= sms) {
         p.stages = (int)((size_t)200 * 1024 / gemm_stage_bytes(dual, bn));
         if (p.stages > kGemmMaxStages) p.stages = kGemmMaxStages;
     }

@@ -82,6 +82,8 @@ struct Engine {
     __half *pf_x = nullptr, *pf_xn = nullptr, *pf_q = nullptr, *pf_attn = nullptr, *pf_h = nullptr;
     float *pf_rope = nullptr;
     int *pf_pos = nullptr;
+    void *pf_ws = nullptr;  // split-K workspace of the projections
+    size_t pf_ws_bytes = 0;
 };
 
 inline Engine *eng(const CudaCache *c) { return c ? static_cast<Engine *>(c->priv) : nullptr; }
@@ -302,7 +304,9 @@ bool prefill_supported(const Engine *e) {
 
 void free_prefill_buffers(Engine *e) {
     cudaFree(e->pf_x); cudaFree(e->pf_xn); cudaFree(e->pf_q); cudaFree(e->pf_attn); cudaFree(e->pf_h);
-    cudaFree(e->pf_rope); cudaFree(e->pf_pos);
+    cudaFree(e->pf_rope); cudaFree(e->pf_pos); cudaFree(e->pf_ws);
+    e->pf_ws = nullptr;
+    e->pf_ws_bytes = 0;
     e->pf_x = e->pf_xn = e->pf_q = e->pf_attn = e->pf_h = nullptr;
     e->pf_rope = nullptr;
     e->pf_pos = nullptr;
@@ -321,6 +325,9 @@ int ensure_prefill_buffers(Engine *e, int rows) {
     LLMB_CUDA_OK(cudaMalloc(&e->pf_h, (size_t)rows * e->ffn * 2));
     LLMB_CUDA_OK(cudaMalloc(&e->pf_rope, (size_t)rows * e->hd * sizeof(float)));
     LLMB_CUDA_OK(cudaMalloc(&e->pf_pos, (size_t)rows * sizeof(int)));
+    e->pf_ws_bytes = 4096 + (size_t)e->sm_count * 131072;
+    LLMB_CUDA_OK(cudaMalloc(&e->pf_ws, e->pf_ws_bytes));
+    LLMB_CUDA_OK(cudaMemsetAsync(e->pf_ws, 0, 4096, e->stream));
     e->pf_rows = rows;
     return LLMB_OK;
 }
@@ -360,6 +367,7 @@ int prefill_rows(Engine *e, int from, int to) {
             g.rope_cs = e->pf_rope;
             g.k_cache = u16w(kl); g.v_cache = u16w(vl);
             g.pos0 = p0; g.max_pos = e->max_seq;
+            g.workspace = e->pf_ws; g.workspace_bytes = e->pf_ws_bytes;
             if ((rc = llmb_gemm_f16(&g, s))) return rc;
             if ((rc = llmb_attn_prefill(u16(e->pf_q), u16(kl), u16(vl), rows, p0, e->nq, e->nkv, e->hd, u16w(e->pf_attn), s)))
                 return rc;
@@ -369,6 +377,7 @@ int prefill_rows(Engine *e, int from, int to) {
             o.c = u16w(e->pf_x);
             o.m = rows; o.n = e->d; o.k = n_q;
             o.epilogue = LLMB_EPI_RESIDUAL;
+            o.workspace = e->pf_ws; o.workspace_bytes = e->pf_ws_bytes;
             if ((rc = llmb_gemm_f16(&o, s))) return rc;
             if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->post_attention_layernorm->d_fp16_tensor), u16w(e->pf_xn), rows,
                                         e->d, c.eps, s)))
@@ -380,6 +389,7 @@ int prefill_rows(Engine *e, int from, int to) {
             f.c = u16w(e->pf_h);
             f.m = rows; f.n = e->ffn; f.k = e->d;
             f.epilogue = LLMB_EPI_SWIGLU;
+            f.workspace = e->pf_ws; f.workspace_bytes = e->pf_ws_bytes;
             if ((rc = llmb_gemm_f16(&f, s))) return rc;
             LlmbGemmArgs dn = {};
             dn.a = u16(e->pf_h);
@@ -387,6 +397,7 @@ int prefill_rows(Engine *e, int from, int to) {
             dn.c = u16w(e->pf_x);
             dn.m = rows; dn.n = e->d; dn.k = e->ffn;
             dn.epilogue = LLMB_EPI_RESIDUAL;
+            dn.workspace = e->pf_ws; dn.workspace_bytes = e->pf_ws_bytes;
             if ((rc = llmb_gemm_f16(&dn, s))) return rc;
         }
         e->launches += 2 + 7 * e->layers;

@@ -101,9 +101,10 @@ def test_gemm_swiglu(pkg, oracle, tile_n):
     assert_close_fp16(host_u16(out).reshape(m, n), want, what="gemm swiglu", abs_tol=tc_tol(want, k))
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128])
-def test_gemm_rope_kv(pkg, oracle, tile_n):
-    hd, nqh, nkvh, k, m, pos0, max_pos = 64, 4, 2, 256, 70, 5, 128
+@pytest.mark.parametrize("tile_n,k,split", [(32, 256, False), (64, 256, False), (128, 256, False), (0, 2048, True)])
+def test_gemm_rope_kv(pkg, oracle, tile_n, k, split):
+    hd, nqh, nkvh, m, pos0, max_pos = 64, 4, 2, 70, 5, 128
+    ws = torch.zeros(4096 + 148 * 131072, dtype=torch.uint8, device="cuda") if split else None
     n_q, n_kv = nqh * hd, nkvh * hd
     n = n_q + 2 * n_kv
     a, b = mats(oracle, m, n, k, 3)
@@ -116,7 +117,8 @@ def test_gemm_rope_kv(pkg, oracle, tile_n):
     kc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
     vc = torch.zeros((max_pos, n_kv), dtype=torch.int16, device="cuda")
     gemm(pkg, a=dev(a), b=dev(b), c=q_out, m=m, n=n, k=k, epilogue=EPI_ROPE_KV, n_q=n_q, n_kv=n_kv, head_dim=hd,
-         rope_cs=dev(cs), k_cache=kc, v_cache=vc, pos0=pos0, max_pos=max_pos, tile_n=tile_n)
+         rope_cs=dev(cs), k_cache=kc, v_cache=vc, pos0=pos0, max_pos=max_pos, tile_n=tile_n,
+         **(dict(workspace=ws, workspace_bytes=ws.numel()) if split else {}))
     y = matmul64(a, b).astype(np.float16).astype(np.float64)
 
     def rope(block, heads):
@@ -139,6 +141,44 @@ def test_gemm_rope_kv(pkg, oracle, tile_n):
                       abs_tol=pair_tol(y[:, n_q:n_q + n_kv]))
     assert_close_fp16(vgot[pos0:pos0 + m], y[:, n_q + n_kv:], what="v", abs_tol=tc_tol(y, k))
     assert not kgot[:pos0].any() and not kgot[pos0 + m:].any() and not vgot[:pos0].any() and not vgot[pos0 + m:].any()
+
+
+def test_gemm_split_k_all_epilogues(pkg, oracle):
+    """Few output tiles and a workspace: K is split across CTAs, partials meet in the workspace, the last
+    CTA of a tile adds them in slice order.  Every epilogue, twice on the same workspace (the arrival
+    counters must come back to zero)."""
+    ws = torch.zeros(4096 + 148 * 131072, dtype=torch.uint8, device="cuda")
+    kw = dict(workspace=ws, workspace_bytes=ws.numel())
+    for rep in range(2):
+        # store
+        m, n, k = 300, 512, 4096
+        a, b = mats(oracle, m, n, k, 10 + rep)
+        out = torch.full((m + 3, n), 0x7BFF, dtype=torch.int16, device="cuda")
+        gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_STORE, **kw)
+        want = matmul64(a, b)
+        got = host_u16(out)
+        assert_close_fp16(got[:m], want, what="split-k store", abs_tol=tc_tol(want, k))
+        assert (got[m:] == 0x7BFF).all()
+        # residual
+        m, n, k = 150, 256, 4096
+        a, b = mats(oracle, m, n, k, 20 + rep)
+        res = oracle.synth_fp16(7, 3, m * n, std=1.0).reshape(m, n)
+        out = dev(res.copy())
+        gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_RESIDUAL, **kw)
+        acc = matmul64(a, b)
+        want = acc.astype(np.float16).astype(np.float64) + f16(res).astype(np.float64)
+        assert_close_fp16(host_u16(out).reshape(m, n), want, what="split-k residual", max_frac=0.1,
+                          abs_tol=np.abs(acc) * 2.0 ** -10 + tc_tol(acc, k))
+        # SwiGLU
+        m, n, k = 130, 384, 2048
+        a, b = mats(oracle, m, n, k, 30 + rep)
+        b2 = oracle.synth_fp16(8, 4, n * k, std=0.02).reshape(n, k)
+        out = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+        gemm(pkg, a=dev(a), b=dev(b), b2=dev(b2), c=out, m=m, n=n, k=k, epilogue=EPI_SWIGLU, **kw)
+        g, u = matmul64(a, b), matmul64(a, b2)
+        want = g / (1.0 + np.exp(-g)) * u
+        assert_close_fp16(host_u16(out).reshape(m, n), want, what="split-k swiglu", abs_tol=tc_tol(want, k))
+        assert not host_u16(ws[:4096].view(torch.int16)).any(), "arrival counters not back to zero"
 
 
 def test_gemm_rejects_unaligned_shapes(pkg):
