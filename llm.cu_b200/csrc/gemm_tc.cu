@@ -20,6 +20,9 @@
 // The SwiGLU variant keeps two accumulators (gate and up, 2 x BN TMEM columns) fed by two B tiles.
 // Rows of A beyond M are zero-filled by TMA and masked in the epilogue; N and K must be multiples
 // of 128 and 64.  Every mbarrier wait is bounded (status word, see llmb_device_status).
+// A launch with few output tiles and a caller-provided workspace splits K over blockIdx.z: partial
+// accumulators are written to the workspace in FP32, and the last CTA of a tile to arrive adds them in
+// slice order and runs the epilogue.
 #include <cuda.h>
 
 #include "common.cuh"
