@@ -192,6 +192,13 @@ int cache_debug_trace(CudaCache *cache, int enable);
  * step is used.  The reference runs its layer loop over all rows on every call
  * (inference.cu:157-186). */
 int cache_set_prefill(CudaCache *cache, int enable, int min_rows);
+/* Samples the next token from the logits the last inference() call left in
+ * Cache->h_token_probdist, the way the reference's inference() does on the host
+ * (sample_next_token, inference.cu:1030-1039; its constants are temperature 0.7, top-k 50,
+ * top-p 0.9).  `draw` numbers the call (one uniform per call from `seed`).  Returns the token, or a
+ * negative status.  The caller appends the token to its array and calls inference() again, as
+ * src/main.cu:121-122 does; the engine then feeds just that token. */
+int cache_sample_next_token(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed, uint64_t draw);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

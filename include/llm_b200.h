@@ -221,6 +221,27 @@ int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache, const uint
 int llmb_iota_i32(int32_t *d_out, int first, int n, llmb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------ */
+/* Host-side temperature / top-k / top-p sampling over the FP16 logits of a step: the        */
+/* arithmetic of sample_next_token (inference.cu:1030-1161), which the reference runs on the  */
+/* host after every step:                                                                     */
+/*   t_i = expf(float(logit_i) / temperature); p_i = t_i / sum(t) (FP32, index order);        */
+/*   order by p descending (ties: lower index first; the reference's qsort leaves ties         */
+/*   unspecified); the first top_k entries are renormalised to sum 1 (the reference's top-k    */
+/*   pass, whose own pick it discards); then the shortest prefix whose running sum reaches     */
+/*   top_p is renormalised and the first entry whose running sum exceeds u is returned         */
+/*   (entry 0 if none does).                                                                  */
+/* Only the first top_k entries are ever ordered unless the prefix runs past them.             */
+/* u in [0, 1) replaces the reference's unseeded rand() / RAND_MAX; llmb_sampler_uniform        */
+/* gives a reproducible one from (seed, draw).  temperature > 0, 1 <= top_k, 0 < top_p <= 1.    */
+/* Like the reference, no maximum is subtracted before expf: a logit / temperature above ~88   */
+/* overflows, which is reported as LLMB_ERR_UNSUPPORTED instead of returning a token.           */
+/* Pure host code: no device is touched.                                                      */
+/* ------------------------------------------------------------------------------------ */
+int llmb_sample_logits_host(const uint16_t *h_logits_fp16, int vocab, float temperature, int top_k, float top_p,
+                            float u, int32_t *token_out);
+float llmb_sampler_uniform(uint64_t seed, uint64_t draw);
+
+/* ------------------------------------------------------------------------------------ */
 /* One whole decode step as a single persistent kernel: every phase of the reference's     */
 /* inference() loop body (inference.cu:149-193) for one new row -- embedding row, per layer */
 /* RMSNorm + QKV + RoPE + cache append, attention over the cache, o_proj + residual,        */

@@ -107,6 +107,11 @@ LLMB_HD int32_t llmb_synth_token(uint64_t key, uint64_t i, int32_t vocab) {
     return (int32_t)(llmb_mix64(key + i) % (uint64_t)vocab);
 }
 
+/* Uniform fp32 in [0, 1) with 24 random bits: exact on every platform. */
+LLMB_HD float llmb_synth_uniform(uint64_t key, uint64_t i) {
+    return (float)(llmb_mix64(key + i) >> 40) * 5.9604644775390625e-08f; /* 2^-24 */
+}
+
 /*
  * Stream ids.  Layer tensors: 16 + 16 * layer + slot, slots in the order below.
  * The order of the slots is the field order of the reference's Llama3Layer struct
@@ -117,6 +122,7 @@ enum {
     LLMB_SID_LM_HEAD = 2,
     LLMB_SID_NORM = 3,
     LLMB_SID_TOKENS = 4,
+    LLMB_SID_SAMPLER = 5,
     LLMB_SLOT_INPUT_LAYERNORM = 0,
     LLMB_SLOT_DOWN = 1,
     LLMB_SLOT_GATE = 2,

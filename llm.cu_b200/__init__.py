@@ -25,14 +25,14 @@ KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
     "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
-    "llmb_rmsnorm_rows", "llmb_attn_prefill", "llmb_iota_i32", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
+    "llmb_rmsnorm_rows", "llmb_attn_prefill", "llmb_iota_i32", "llmb_sample_logits_host", "llmb_sampler_uniform", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
     "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
-    "cache_kernel_launches", "cache_set_prefill",
+    "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token",
 ]
 
 
@@ -125,6 +125,9 @@ def _declare(l):
     l.llmb_rmsnorm_rows.argtypes = [vp, vp, vp, i32, i32, C.c_double, vp]
     l.llmb_attn_prefill.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
     l.llmb_iota_i32.argtypes = [vp, i32, i32, vp]
+    l.llmb_sample_logits_host.argtypes = [vp, i32, C.c_float, i32, C.c_float, C.c_float, C.POINTER(C.c_int32)]
+    l.llmb_sampler_uniform.argtypes = [u64, u64]
+    l.llmb_sampler_uniform.restype = C.c_float
     M, K = C.POINTER(Llama3Struct), C.POINTER(CudaCacheStruct)
     l.init_llama3.argtypes = [i32]
     l.init_llama3.restype = M
@@ -170,6 +173,7 @@ def _declare(l):
     l.cache_debug_trace.argtypes = [K, i32]
     l.cache_kernel_launches.argtypes = [K]
     l.cache_set_prefill.argtypes = [K, i32, i32]
+    l.cache_sample_next_token.argtypes = [K, C.c_float, i32, C.c_float, u64, u64]
     l.cache_kernel_launches.restype = C.c_longlong
 
 

@@ -22,6 +22,7 @@ SOURCES = [
     "host/model.cu",
     "host/engine.cu",
     "host/safetensor.cpp",
+    "host/sampler.cpp",
 ]
 HEADERS = [
     "csrc/common.cuh",

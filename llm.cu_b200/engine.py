@@ -122,6 +122,14 @@ class Cache:
         buf = (C.c_uint16 * self.vocab).from_address(self.ptr.contents.h_token_probdist)
         return np.frombuffer(buf, dtype=np.uint16).copy()
 
+    def sample(self, temperature=0.7, top_k=50, top_p=0.9, seed=0, draw=0):
+        """Temperature / top-k / top-p sample from the logits of the last infer() call (the reference's host
+        sampler and its default constants); `draw` numbers the call."""
+        r = lib.cache_sample_next_token(self.ptr, temperature, top_k, top_p, seed, draw)
+        if r < 0:
+            check(-r, "cache_sample_next_token")
+        return r
+
     def enable_hidden_dump(self, on=True):
         check(lib.cache_enable_hidden_dump(self.ptr, 1 if on else 0), "cache_enable_hidden_dump")
 

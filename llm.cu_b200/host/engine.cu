@@ -752,6 +752,24 @@ extern "C" int cache_set_prefill(CudaCache *cache, int enable, int min_rows) {
     return LLMB_OK;
 }
 
+extern "C" int cache_sample_next_token(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed,
+                                       uint64_t draw) {
+    Engine *e = eng(cache);
+    if (!e || !cache->h_token_probdist) return -LLMB_ERR_INVALID;
+    if (!e->copy_logits || e->consumed.empty()) {
+        set_last_error("cache_sample_next_token: no logits on the host (run inference() with copy_logits on first)");
+        return -LLMB_ERR_INVALID;
+    }
+    if (e->tp_size > 1) {
+        set_last_error("cache_sample_next_token: a tensor-parallel rank holds a slice of the logits only");
+        return -LLMB_ERR_UNSUPPORTED;
+    }
+    int32_t token = -1;
+    const int rc = llmb_sample_logits_host(reinterpret_cast<const uint16_t *>(cache->h_token_probdist), e->vocab, temperature,
+                                           top_k, top_p, llmb_sampler_uniform(seed, draw), &token);
+    return rc ? -rc : token;
+}
+
 extern "C" long long cache_kernel_launches(const CudaCache *cache) {
     const Engine *e = eng(cache);
     return e ? e->launches : -1;

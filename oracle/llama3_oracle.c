@@ -285,6 +285,68 @@ int oracle_argmax_fp16(const uint16_t *logits, int n) {
     return best;
 }
 
+/*
+ * inference.cu:1030-1161 (sample_next_token and its helpers), statement by statement, on a full
+ * sorted copy of the distribution.  Two things are pinned down that the reference leaves open:
+ * ties in the descending order go to the lower index (its qsort comparator returns 0 for them),
+ * and the uniform number is an argument (it calls an unseeded rand()).  The top-k pass still
+ * renormalises the first k entries in place before the top-p pass reads them; its own pick is
+ * discarded there and not computed here.
+ */
+typedef struct { float probability; int index; } OracleProbIndex;
+
+static int cmp_prob_desc(const void *a, const void *b) {
+    const OracleProbIndex *x = (const OracleProbIndex *)a, *y = (const OracleProbIndex *)b;
+    if (x->probability < y->probability) return 1;
+    if (x->probability > y->probability) return -1;
+    return (x->index > y->index) - (x->index < y->index);
+}
+
+int oracle_sample(const uint16_t *logits, int vocab, float temperature, int top_k, float top_p, float u) {
+    OracleProbIndex *d = (OracleProbIndex *)malloc(sizeof(OracleProbIndex) * (size_t)vocab);
+    float *t = (float *)malloc(sizeof(float) * (size_t)vocab);
+    if (!d || !t) { free(d); free(t); return -1; }
+    float cumsum = 0.0f;
+    for (int i = 0; i < vocab; ++i) { /* :1044-1050 */
+        float scaled = h2f(logits[i]) / temperature;
+        t[i] = expf(scaled);
+        cumsum += t[i];
+    }
+    for (int i = 0; i < vocab; ++i) { /* :1052-1057 */
+        t[i] /= cumsum;
+        d[i].probability = t[i];
+        d[i].index = i;
+    }
+    qsort(d, (size_t)vocab, sizeof(OracleProbIndex), cmp_prob_desc); /* :1059 */
+    int k = top_k > vocab ? vocab : top_k; /* :1083-1085 */
+    float sum = 0.0f;
+    for (int i = 0; i < k; ++i) sum += d[i].probability;  /* :1088-1091 */
+    for (int i = 0; i < k; ++i) d[i].probability /= sum;  /* :1094-1096 */
+    float p = top_p > 1.0f ? 1.0f : top_p; /* :1124-1126 */
+    float cumulative = 0.0f;
+    int cutoff = 0;
+    for (; cutoff < vocab; ++cutoff) { /* :1131-1136 */
+        cumulative += d[cutoff].probability;
+        if (cumulative >= p) break;
+    }
+    sum = cumulative;
+    if (cutoff >= vocab) cutoff = vocab - 1; /* :1140-1143 */
+    for (int i = 0; i <= cutoff; ++i) d[i].probability /= sum; /* :1146-1148 */
+    int token = d[0].index; /* :1159-1160 */
+    cumulative = 0.0f;
+    for (int i = 0; i <= cutoff; ++i) { /* :1154-1158 */
+        cumulative += d[i].probability;
+        if (u < cumulative) { token = d[i].index; break; }
+    }
+    free(d);
+    free(t);
+    return token;
+}
+
+float oracle_sampler_uniform(uint64_t seed, uint64_t draw) {
+    return llmb_synth_uniform(llmb_stream_key(seed, LLMB_SID_SAMPLER), draw);
+}
+
 /* ------------------------------------------------------------------------------------ */
 /* KV-cached decoder (timed CPU baseline; same rounding points, vectorised sums)         */
 /* ------------------------------------------------------------------------------------ */

@@ -70,6 +70,9 @@ int oracle_forward(const OracleConfig *cfg, const uint16_t *const *weights, cons
 
 /* First maximum over FP16 logits (NaN never wins), the tie-break the engine must match. */
 int oracle_argmax_fp16(const uint16_t *logits, int n);
+/* inference.cu:1030-1161 with ties to the lower index and the uniform number as an argument. */
+int oracle_sample(const uint16_t *logits, int vocab, float temperature, int top_k, float top_p, float u);
+float oracle_sampler_uniform(uint64_t seed, uint64_t draw);
 
 /*
  * KV-cached decode used as the timed CPU baseline: same rounding points, but dot products are

@@ -72,6 +72,9 @@ def lib():
         l.oracle_bf16_to_fp16.restype = None
         l.oracle_forward.argtypes = [C.POINTER(OracleConfig), vp, vp, C.c_int, C.c_int, vp, vp]
         l.oracle_argmax_fp16.argtypes = [vp, C.c_int]
+        l.oracle_sample.argtypes = [vp, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float]
+        l.oracle_sampler_uniform.argtypes = [C.c_uint64, C.c_uint64]
+        l.oracle_sampler_uniform.restype = C.c_float
         l.oracle_decoder_new.argtypes = [C.POINTER(OracleConfig), vp, C.c_int]
         l.oracle_decoder_new.restype = vp
         l.oracle_decoder_free.argtypes = [vp]

@@ -173,3 +173,25 @@ def test_sequence_longer_than_cache_is_rejected(pkg, oracle):
         cache.greedy(list(range(20)), 20)
     cache.close()
     model.close()
+
+
+def test_host_sampler_on_engine_logits(pkg, oracle, tiny_weights):
+    """inference() leaves FP16 logits on the host; the sampler draws from them as the reference's host
+    sampler does, and the sampled token fed back continues the sequence through the cache."""
+    cfg = pkg.CONFIGS["tiny"]
+    seq = oracle.synth_tokens(0, 12, cfg.vocab).tolist()
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=64)
+    cache = pkg.Cache(model)
+    launches = []
+    for draw in range(4):
+        greedy = cache.infer(seq)
+        logits = cache.logits()
+        tok = cache.sample(temperature=0.7, top_k=50, top_p=0.9, seed=3, draw=draw)
+        u = float(oracle.lib().oracle_sampler_uniform(3, draw))
+        assert tok == int(oracle.lib().oracle_sample(logits.ctypes.data, cfg.vocab, 0.7, 50, 0.9, u))
+        assert cache.sample(temperature=0.7, top_k=1, top_p=0.9, seed=3, draw=draw) == greedy
+        seq.append(tok)
+        launches.append(cache.kernel_launches())
+    assert launches[1] - launches[0] == 1  # an appended sampled token costs one decode step
+    cache.close()
+    model.close()
