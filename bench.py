@@ -35,6 +35,9 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_tokens_per_s_bs1"
 UNIT = "tok/s"
 PROMPT = 128
+# decode_step_kernel, ncu --set full on the 4-layer / 32K-vocabulary case: (dram__bytes_read.sum +
+# dram__bytes_write.sum) / algorithmic bytes = (2.01396 GB + 20.8 MB) / 2.01367 GB
+NCU_TRAFFIC_RATIO = 1.0105
 SEED = 0
 
 
@@ -207,7 +210,12 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_source": peak_src,
+                     "traffic": (alg_bytes * NCU_TRAFFIC_RATIO) if (world == 1 and not args.per_op_kernels) else None,
+                     "traffic_source": ("scaled from the ncu capture of the 4-layer case of the same kernel "
+                                        "(dram read + write = %.4f x algorithmic bytes there; traffic is proportional "
+                                        "to the weight and cache bytes streamed)" % NCU_TRAFFIC_RATIO)
+                                       if (world == 1 and not args.per_op_kernels) else None,
+                     "peak_source": peak_src,
                      "scope": ("whole decode step: one kernel per fused op, 163 launches in a CUDA graph" if args.per_op_kernels else
                                "decode_step_kernel: one persistent launch per token") +
                               "; algorithmic bytes per launch and GPU = weight bytes %d + %d per cached row" % (
