@@ -229,8 +229,8 @@ static int derive_config(Llama3 *m) {
     return LLMB_OK;
 }
 
-// The window of a tensor that tensor-parallel rank `rank` of `size` keeps (SURVEY 8e of the task:
-// q/k/v, gate/up and lm_head by output rows, o_proj and down_proj by input columns, the rest whole).
+// The window of a tensor that tensor-parallel rank `rank` of `size` keeps: q/k/v, gate/up and
+// lm_head by output rows, o_proj and down_proj by input columns, the rest whole.
 struct Shard {
     int row0, rows, col0, cols, full_cols;
     size_t elems() const { return (size_t)rows * cols; }
