@@ -105,6 +105,17 @@ def load_package():
     return ge.load_package()
 
 
+def load_configs():
+    """The named model shapes without the product library: configs.py is pure Python, and the reference arm
+    must not map libllm_b200.so into its process."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("llm_cu_b200_configs", os.path.join(ROOT, "llm.cu_b200", "configs.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod   # dataclasses resolves the module by name while the class is built
+    spec.loader.exec_module(mod)
+    return mod.CONFIGS
+
+
 def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
@@ -275,9 +286,8 @@ def run_reference(args):
     if not os.path.exists(harness):
         print(json.dumps(dict(base, unavailable="oracle/_ref/ref_harness was not built (reference tree absent at build time)")))
         return
-    pkg = load_package()
     from oracle import oracle_lib as oracle
-    cfg = pkg.CONFIGS[args.config]
+    cfg = load_configs()[args.config]
     steps = min(args.steps, args.ref_max_steps)
     warm = min(max(args.warmup, 1), 2)
     need = cfg.weight_bytes_per_token() + (1 << 30)

@@ -152,6 +152,9 @@ int cache_set_options(CudaCache *cache, int use_graph, int use_pdl, int copy_log
  * = one persistent kernel per token (llmb_decode_step); 0 = one kernel per fused operation,
  * captured into a CUDA graph (llmb_gemv_f16, llmb_attn_decode, ...). */
 int cache_use_step_kernel(CudaCache *cache, int enable);
+/* Spin limit of the step kernel's waits for tensor-parallel peers (0 = default, about a second): a rank
+ * whose peer does not deliver within it gives up with LLMB_ERR_TIMEOUT instead of waiting on. */
+int cache_set_tp_poll_limit(CudaCache *cache, unsigned int tag_poll_limit);
 /* Tensor parallel decode, one process per GPU (llama3_set_tp before loading): each rank exports a
  * 64-byte CUDA IPC handle of its exchange block with cache_tp_handle(); the caller gathers all
  * ranks' handles in rank order (torch.distributed, MPI, ...) and passes the tp_size * 64 bytes to

@@ -148,8 +148,10 @@ int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint1
 /* which allocates every buffer with cudaMalloc in init_cache (inference.cu:101-145).           */
 /* Limits: n_q_heads * n_splits <= 4096, head_dim <= 128, n_kv_heads <= 64; larger requests     */
 /* return LLMB_ERR_UNSUPPORTED.  The first call on each device resolves the array's address and  */
-/* should be made before any stream capture begins.  Calls on one device share the array: calls */
-/* that may run concurrently on the GPU race.  Allocates nothing.                               */
+/* should be made before any stream capture begins; if the library's device code is not yet     */
+/* resident on that device, that first call is also what makes the CUDA runtime load it (array   */
+/* and kernels), so make it at start-up.  Calls on one device share the array: calls that may    */
+/* run concurrently on the GPU race.  Calls no cudaMalloc, cudaFree or allocating routine.       */
 int llmb_attn_decode_static(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
                             const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
                             int split_len, uint16_t *d_out, int use_pdl, llmb_stream_t stream);
@@ -253,7 +255,7 @@ float llmb_sampler_uniform(uint64_t seed, uint64_t draw);
 /*   history[pos + 1] are written; pos is advanced by one.                                   */
 /*   scratch: llmb_decode_step_scratch_bytes() bytes, 256-byte aligned, zeroed once before   */
 /*   the first launch and whenever llmb_device_status() reports a non-zero status.           */
-/*   split_len must be a multiple of 64; n_splits * split_len >= pos + 1.                    */
+/*   split_len must be a multiple of 32; n_splits * split_len >= pos + 1.                    */
 /* ------------------------------------------------------------------------------------ */
 typedef struct {
     const uint16_t *wqkv;   /* [(n_q + 2 n_kv)][d_model]: q, k, v rows back to back */
@@ -298,6 +300,8 @@ typedef struct {
                                stamps, one row per CTA; per phase: consumers entered, dependency met, input
                                ready, done; finisher started, first stage, last stage, fenced.  NULL in
                                production. */
+    uint32_t tag_poll_limit; /* tensor parallel: spins a wait for peer data may take before the kernel gives
+                                up with status 205-207; 0 = 2^20 (about a second) */
 } LlmbDecodeStepArgs;
 
 size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits);

@@ -31,7 +31,7 @@ HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
-    "cache_set_options", "cache_use_step_kernel", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
+    "cache_set_options", "cache_use_step_kernel", "cache_set_tp_poll_limit", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
     "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token",
 ]
 
@@ -103,6 +103,24 @@ class GemmArgs(C.Structure):
     ]
 
 
+class LayerArgs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wqkv", "wo", "wgate", "wup", "wdown", "g_in", "g_post", "k_cache", "v_cache")]
+
+
+class DecodeStepArgs(C.Structure):
+    _fields_ = [("layers", C.c_void_p)] + [
+        (n, C.c_int) for n in ("n_layers", "d_model", "n_q_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "embed_rows",
+                               "max_pos")] + [
+        ("rope_theta", C.c_float), ("eps", C.c_double), ("embed", C.c_void_p), ("lm_head", C.c_void_p),
+        ("g_final", C.c_void_p), ("history", C.c_void_p), ("history_len", C.c_int), ("pos", C.c_void_p),
+        ("x", C.c_void_p), ("q", C.c_void_p), ("attn", C.c_void_p), ("h", C.c_void_p), ("logits", C.c_void_p),
+        ("next_token", C.c_void_p), ("scratch", C.c_void_p), ("max_splits", C.c_int), ("n_splits", C.c_int),
+        ("split_len", C.c_int), ("with_logits", C.c_int), ("hidden", C.c_void_p), ("tp_rank", C.c_int),
+        ("tp_size", C.c_int), ("vocab_offset", C.c_int), ("x_alt", C.c_void_p), ("peers", C.c_void_p * 8),
+        ("trace", C.c_void_p), ("tag_poll_limit", C.c_uint32),
+    ]
+
+
 def _declare(l):
     vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
     l.llmb_last_error.restype = C.c_char_p
@@ -157,6 +175,7 @@ def _declare(l):
     l.cache_reset.argtypes = [K]
     l.cache_set_options.argtypes = [K, i32, i32, i32]
     l.cache_use_step_kernel.argtypes = [K, i32]
+    l.cache_set_tp_poll_limit.argtypes = [K, C.c_uint]
     l.cache_tp_handle.argtypes = [K, vp]
     l.cache_tp_connect.argtypes = [K, vp]
     l.llmb_decode_step_exchange_bytes.argtypes = [i32, i32]
@@ -164,7 +183,7 @@ def _declare(l):
     l.cache_enable_hidden_dump.argtypes = [K, i32]
     l.llmb_decode_step_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.llmb_decode_step_scratch_bytes.restype = sz
-    l.llmb_decode_step.argtypes = [vp, vp]
+    l.llmb_decode_step.argtypes = [C.POINTER(DecodeStepArgs), vp]
     l.cache_read_hidden.argtypes = [K, vp]
     l.inference_greedy.argtypes = [M, K, C.POINTER(C.c_int), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_float),
                                    C.POINTER(C.c_float)]
@@ -194,5 +213,5 @@ def check(code, where):
 from .configs import CONFIGS, ModelConfig  # noqa: E402
 from .engine import Cache, Model  # noqa: E402
 
-__all__ = ["lib", "check", "LlmbError", "Llama3Config", "GemvArgs", "GemmArgs", "Model", "Cache", "CONFIGS", "ModelConfig",
+__all__ = ["lib", "check", "LlmbError", "Llama3Config", "GemvArgs", "GemmArgs", "LayerArgs", "DecodeStepArgs", "Model", "Cache", "CONFIGS", "ModelConfig",
            "KERNEL_SYMBOLS", "HOST_SYMBOLS", "LIB_PATH"]

@@ -216,12 +216,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 template <int HD, int G>
 static int launch_attn(const AttnParams &p, bool pdl, cudaStream_t stream) {
     constexpr size_t smem = (size_t)2 * kTile * HD * sizeof(__half);
-    static bool attr_set = false;
-    if (!attr_set) {
-        LLMB_CUDA_OK(cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem));
-        attr_set = true;
-    }
+    static size_t attr_set[kMaxDevices] = {};  // per instantiation and device
+    LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, smem));
     LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads), dim3(kAttnThreads), smem,
                             stream, pdl, p));
     return LLMB_OK;
@@ -295,7 +291,10 @@ extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, 
 //    2,130,176 bytes and every GPU that loads the library carries it until the process ends.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress:
 //    in host code the array's name is only a handle, not something a kernel can dereference)
-//    and remembers it; make that first call before starting any stream capture.
+//    and remembers it; make that first call before starting any stream capture.  If the
+//    library's device code has not been loaded on that device yet, this look-up is what makes
+//    the CUDA runtime load it (the array and the kernels then take their place in device
+//    memory), so make the first call at start-up, not inside the allocation-free region.
 //  * All calls on a device share the one array and it keeps whatever the previous call
 //    left, so the arrival counters are cleared on the stream before each launch; two calls
 //    that can overlap on the GPU (different streams, no dependency) race on it.
@@ -348,6 +347,11 @@ extern "C" int llmb_attn_decode_static(const uint16_t *d_q, const uint16_t *d_k_
             "head_dim <= 128, n_kv_heads <= 64); use llmb_attn_decode with a caller-provided workspace");
         return LLMB_ERR_UNSUPPORTED;
     }
+    // the argument checks llmb_attn_decode makes, here already: nothing is queued on the stream for a call
+    // that is going to be refused
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out) return LLMB_ERR_INVALID;
+    if (split_len <= 0 || n_q_heads % n_kv_heads) return LLMB_ERR_INVALID;
+    if (((uintptr_t)d_k_cache & 15) || ((uintptr_t)d_v_cache & 15)) return LLMB_ERR_INVALID;
     void *scratch = nullptr;
     int rc = static_scratch_ptr(&scratch);
     if (rc) return rc;

@@ -25,6 +25,24 @@ int cuda_fail(cudaError_t e, const char *file, int line);
 void set_last_error(const char *msg);
 int sm_count_cached();
 
+// A kernel's opt-in to more than 48 KB of dynamic shared memory is a per-device attribute.  `have` is a
+// per-kernel table indexed by device ordinal; returns true when the current device's entry is below
+// `bytes` (the caller then sets the attribute and records it with smem_attr_set).
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t (&have)[kMaxDevices], size_t bytes) {
+    const int dev = current_device_slot();
+    if (dev >= 0 && have[dev] >= bytes) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && dev >= 0) have[dev] = bytes;
+    return e;
+}
+
 // ---------------------------------------------------------------------------------------
 // Device side
 // ---------------------------------------------------------------------------------------

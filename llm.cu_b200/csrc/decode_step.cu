@@ -49,7 +49,7 @@ constexpr uint32_t kDsSlotBytes = 32 * 1024;
 constexpr int kDsJ = 8;                           // 16-byte chunks of x per thread: k <= 16384
 constexpr int kDsTile = 32;                       // cache rows per attention tile
 constexpr uint32_t kPollLimit = 1u << 22;
-constexpr uint32_t kTagPollLimit = 1u << 20;  // tagged peer data: on the order of a second
+constexpr uint32_t kTagPollLimit = 1u << 20;  // default spins of a tagged wait: on the order of a second
 
 struct DsLayer {
     const __half *wqkv, *wo, *wgate, *wup, *wdown, *g_in, *g_post;
@@ -74,6 +74,7 @@ struct DsParams {
     float rope_theta;
     int n_layers, d, nq, nkv, hd, ffn, vocab, embed_rows, max_pos;
     int n_splits, split_len, with_logits, history_len;
+    uint32_t tag_poll_limit;    // spins a tagged wait may take before it gives up
     // tensor parallel: nq, nkv, ffn and vocab above are this rank's shares
     int tp_rank, tp_size, vocab_offset;
     __half *x_alt;              // second residual-stream buffer (ping-pong across all-reduces)
@@ -89,7 +90,13 @@ struct DsParams {
 //                and its tag travel in one 8-byte store, and a reader spins until the tag is the number
 //                of the all-reduce it is performing, so no fence, flag or barrier stands between a
 //                projection and the all-reduced row (the low-latency protocol of collective libraries).
+//   then         row[2][d_model / 2] of (two FP16 values, 32-bit tag): the all-reduced residual row,
+//                written only by this rank.  Each 16-byte chunk of the row has one owner CTA, which
+//                alone polls the tp_size partial sums, adds them in rank order and publishes the chunk
+//                here with the same tag; every other CTA polls d_model * 4 local bytes instead of
+//                tp_size * d_model * 8 bytes of partial sums.
 constexpr size_t kTpFlagsOff = 0, kTpBestOff = 256, kTpRecvOff = 512;
+__host__ __device__ constexpr size_t tp_row_off(int tp_size, int d) { return kTpRecvOff + (size_t)2 * tp_size * d * 8; }
 
 enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
 
@@ -211,12 +218,13 @@ struct DsCursor {
     uint32_t it;
 };
 
-// Requests the next ring stage, walking on through the projections in program order.
+// Walks the cursor on to the next ring stage in program order (through the projections of the step)
+// and yields its source span(s).  False once the last stage of the step has been handed out.
 template <bool kTp>
-__device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv,
-                                                 unsigned char *ring, uint64_t *full_bar, uint64_t policy) {
+__device__ __forceinline__ bool cursor_next(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv,
+                                            const unsigned char *&src, const unsigned char *&src2, uint32_t &bytes) {
     while (c.rg >= c.rg_end) {
-        if (c.ph + 1 >= n_gemv) { c.ph = n_gemv; return; }
+        if (c.ph + 1 >= n_gemv) { c.ph = n_gemv; return false; }
         ++c.ph;
         const GemvDesc g = gemv_desc<kTp>(p, layers, c.ph, emb);
         c.w = reinterpret_cast<const unsigned char *>(g.w);
@@ -226,16 +234,28 @@ __device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLaye
         c.R = g.R;
         cta_range((g.n + g.R - 1) / g.R, c.rg, c.rg_end);
     }
-    const int s = c.it % kDsSlots;
     const int row0 = c.rg * c.R;
     const int rows = min(c.R, c.n - row0);
-    unsigned char *dst = ring + (size_t)s * kDsSlotBytes;
-    const uint32_t bytes = (uint32_t)(rows * c.row_bytes);
-    mbar_arrive_expect_tx(&full_bar[s], c.w2 ? 2 * bytes : bytes);
-    bulk_g2s(dst, c.w + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
-    if (c.w2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, c.w2 + (size_t)row0 * c.row_bytes, bytes, &full_bar[s], policy);
-    ++c.it;
+    bytes = (uint32_t)(rows * c.row_bytes);
+    src = c.w + (size_t)row0 * c.row_bytes;
+    src2 = c.w2 ? c.w2 + (size_t)row0 * c.row_bytes : nullptr;
     ++c.rg;
+    return true;
+}
+
+// Requests the next ring stage.
+template <bool kTp>
+__device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv,
+                                                 unsigned char *ring, uint64_t *full_bar, uint64_t policy) {
+    const unsigned char *src, *src2;
+    uint32_t bytes;
+    if (!cursor_next<kTp>(p, layers, emb, c, n_gemv, src, src2, bytes)) return;
+    const int s = c.it % kDsSlots;
+    unsigned char *dst = ring + (size_t)s * kDsSlotBytes;
+    mbar_arrive_expect_tx(&full_bar[s], src2 ? 2 * bytes : bytes);
+    bulk_g2s(dst, src, bytes, &full_bar[s], policy);
+    if (src2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, src2, bytes, &full_bar[s], policy);
+    ++c.it;
 }
 
 template <int NR>
@@ -509,61 +529,78 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         } else {
             // Tensor parallel: the input row is the all-reduced projection plus the previous residual
             // row, x = half(float(half(sum over ranks of partials)) + float(x_old)): the reference's
-            // rounding points (inference.cu:445, :385-387) with the sum taken in rank order.  Every CTA
-            // forms the whole row for itself; the chunk's owner CTA also stores it for later residual adds.
+            // rounding points (inference.cu:445, :385-387) with the sum taken in rank order.
+            // (1) The owner CTA of a 16-byte chunk (chunk % gridDim.x) forms it: four threads of group 0
+            //     per chunk, two elements each, poll the tp_size tagged partial sums of their elements.
+            // (2) It stores the chunk into the residual buffer and publishes it, tagged, in the local row.
+            // (3) Every thread of every CTA polls its own chunks of the local row.
             const unsigned char *recv = p.peer[p.tp_rank] + kTpRecvOff + (size_t)(g.reduce & 1) * p.tp_size * p.d * 8;
+            unsigned char *row = p.peer[p.tp_rank] + tp_row_off(p.tp_size, p.d) + (size_t)(g.reduce & 1) * p.d * 4;
             const unsigned int tag = tag_base + (unsigned int)g.reduce + 1u;
+            if (grp == 0) {
+                const int c = (int)blockIdx.x + (int)gridDim.x * (gtid >> 2);
+                if (c < (p.d >> 3)) {
+                    const int e0 = c * 8 + (gtid & 3) * 2;
+                    float a0 = 0.0f, a1 = 0.0f;
+                    for (int r = 0; r < p.tp_size; ++r) {
+                        const unsigned char *src = recv + ((size_t)r * p.d + (size_t)e0) * 8;
+                        uint4 q;
+                        uint32_t spins = 0;
+                        for (;;) {
+                            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                                         : "l"(src)
+                                         : "memory");
+                            if ((q.y == tag && q.w == tag) || !ok) break;
+                            if ((++spins & 63u) == 0) {  // another wait of this CTA gave up: do not start a new limit
+                                if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
+                                if (spins > p.tag_poll_limit) {
+                                    atomicExch(p.status, 205);
+                                    sh.abort_flag = 1;
+                                    break;
+                                }
+                            }
+                        }
+                        a0 += __uint_as_float(q.x);
+                        a1 += __uint_as_float(q.z);
+                    }
+                    const float2 xo = __half22float2(*reinterpret_cast<const __half2 *>(g.x_old + e0));
+                    const __half2 xn = __halves2half2(__float2half_rn(__half2float(__float2half_rn(a0)) + xo.x),
+                                                      __float2half_rn(__half2float(__float2half_rn(a1)) + xo.y));
+                    *reinterpret_cast<__half2 *>(g.x_new + e0) = xn;
+                    if (g.hidden_row) *reinterpret_cast<__half2 *>(g.hidden_row + e0) = xn;
+                    asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(row + (size_t)(e0 >> 1) * 8),
+                                 "r"(*reinterpret_cast<const uint32_t *>(&xn)), "r"(tag)
+                                 : "memory");
+                }
+            }
 #pragma unroll
             for (int j = 0; j < kDsJ / 2; ++j) {
                 xh[j] = make_uint4(0, 0, 0, 0);
                 if (have[j]) {
-                    const int c = gtid + kDsGThreads * j;
-                    float acc8[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc8[e] = 0.0f;
-                    for (int r = 0; r < p.tp_size; ++r) {
-                        // eight (value, tag) pairs = four 16-byte loads; spin until every tag is this all-reduce's
-                        const unsigned char *src = recv + ((size_t)r * p.d + (size_t)c * 8) * 8;
-                        uint4 q[4];
-                        uint32_t spins = 0;
-                        for (;;) {
-                            bool all = true;
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                             : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
-                                             : "l"(src + 16 * u)
-                                             : "memory");
-                                all = all && q[u].y == tag && q[u].w == tag;
-                            }
-                            if (all || !ok) break;
-                            if (++spins > kTagPollLimit) {
+                    const unsigned char *src = row + (size_t)(gtid + kDsGThreads * j) * 32;  // 4 (FP16 pair, tag) slots
+                    uint4 q0, q1;
+                    uint32_t spins = 0;
+                    for (;;) {
+                        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(q0.x), "=r"(q0.y), "=r"(q0.z), "=r"(q0.w)
+                                     : "l"(src)
+                                     : "memory");
+                        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(q1.x), "=r"(q1.y), "=r"(q1.z), "=r"(q1.w)
+                                     : "l"(src + 16)
+                                     : "memory");
+                        if ((q0.y == tag && q0.w == tag && q1.y == tag && q1.w == tag) || !ok) break;
+                        if ((++spins & 63u) == 0) {
+                            if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
+                            if (spins > p.tag_poll_limit) {
                                 atomicExch(p.status, 205);
                                 sh.abort_flag = 1;
                                 break;
                             }
                         }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            acc8[2 * u] += __uint_as_float(q[u].x);
-                            acc8[2 * u + 1] += __uint_as_float(q[u].z);
-                        }
                     }
-                    const uint4 xo = __ldcg(reinterpret_cast<const uint4 *>(g.x_old) + c);
-                    float xf[8];
-                    unpack8(xo, xf);
-                    uint4 xn;
-                    __half2 *o = reinterpret_cast<__half2 *>(&xn);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        o[e] = __halves2half2(
-                            __float2half_rn(__half2float(__float2half_rn(acc8[2 * e])) + xf[2 * e]),
-                            __float2half_rn(__half2float(__float2half_rn(acc8[2 * e + 1])) + xf[2 * e + 1]));
-                    xh[j] = xn;
-                    if (grp == 0 && (c % (int)gridDim.x) == (int)blockIdx.x) {
-                        reinterpret_cast<uint4 *>(g.x_new)[c] = xn;
-                        if (g.hidden_row) reinterpret_cast<uint4 *>(g.hidden_row)[c] = xn;
-                    }
+                    xh[j] = make_uint4(q0.x, q0.z, q1.x, q1.z);
                 }
             }
 #pragma unroll
@@ -843,13 +880,16 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                              : "l"(recv + (size_t)i * 16)
                              : "memory");
                 if (q.y == tag && q.w == tag) break;
-                if (++spins > kTagPollLimit) {
-                    atomicExch(p.status, 207);
-                    sh.abort_flag = 1;
-                    break;
+                if ((++spins & 63u) == 0) {
+                    if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
+                    if (spins > p.tag_poll_limit) {
+                        atomicExch(p.status, 207);
+                        sh.abort_flag = 1;
+                        break;
+                    }
                 }
             }
-            if (sh.abort_flag) break;
+            if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
         }
     }
 
@@ -884,7 +924,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     for (int r = 0; r < p.tp_size; ++r)
                         if (r != p.tp_rank)
                             *reinterpret_cast<volatile unsigned long long *>(p.peer[r] + kTpFlagsOff + 8 * p.tp_rank) = seq;
-                    bool fine = true;
+                    bool fine = ok;  // after a wait that gave up, the peers are not waited for either
                     for (int r = 0; r < p.tp_size && fine; ++r) {
                         if (r == p.tp_rank) continue;
                         const unsigned long long *f = reinterpret_cast<const unsigned long long *>(p.peer[p.tp_rank] + kTpFlagsOff + 8 * r);
@@ -892,10 +932,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                         uint32_t polls = 0;
                         do {
                             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(fv) : "l"(f) : "memory");
-                            if (++polls > kPollLimit) { fine = false; break; }
+                            if (++polls > p.tag_poll_limit) { fine = false; break; }
                         } while (fv < seq);
                     }
-                    if (!fine) atomicExch(p.status, 206);
+                    if (!fine && ok) atomicExch(p.status, 206);
                     v = -INFINITY;
                     idx = 0x7fffffff;
                     for (int r = 0; r < p.tp_size; ++r) {
@@ -933,7 +973,7 @@ static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 extern "C" size_t llmb_decode_step_exchange_bytes(int tp_size, int d_model) {
     if (tp_size < 1 || d_model <= 0) return 0;
-    return kTpRecvOff + (size_t)2 * tp_size * d_model * 8;
+    return tp_row_off(tp_size, d_model) + (size_t)2 * d_model * 4;
 }
 
 extern "C" size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {
@@ -1006,6 +1046,7 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
     p.split_len = a->split_len;
     p.with_logits = a->with_logits;
     p.history_len = a->history_len;
+    p.tag_poll_limit = a->tag_poll_limit ? a->tag_poll_limit : kTagPollLimit;
     p.tp_rank = 0;
     p.tp_size = 1;
     p.vocab_offset = 0;
@@ -1024,20 +1065,19 @@ extern "C" int llmb_decode_step(const LlmbDecodeStepArgs *a, llmb_stream_t strea
 
     const size_t smem = (size_t)kDsSlots * kDsSlotBytes + (size_t)2 * kDsTile * 128 * sizeof(__half) +
                         (size_t)a->n_layers * sizeof(DsLayer);
-    static size_t smem_limit = 0, smem_set = 0;
-    if (!smem_limit) {
+    static size_t smem_limit[kMaxDevices] = {}, set_plain[kMaxDevices] = {}, set_tp[kMaxDevices] = {};  // per device
+    const int slot = current_device_slot();
+    if (slot < 0) return LLMB_ERR_UNSUPPORTED;
+    if (!smem_limit[slot]) {
         cudaFuncAttributes fa;
         int optin = 0;
         LLMB_CUDA_OK(cudaFuncGetAttributes(&fa, decode_step_kernel<true>));
         LLMB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        smem_limit = (size_t)optin > fa.sharedSizeBytes ? (size_t)optin - fa.sharedSizeBytes : 0;
+        smem_limit[slot] = (size_t)optin > fa.sharedSizeBytes ? (size_t)optin - fa.sharedSizeBytes : 1;
     }
-    if (smem > smem_limit) return LLMB_ERR_UNSUPPORTED;  // too many layers for the shared-memory table
-    if (smem > smem_set) {
-        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        LLMB_CUDA_OK(cudaFuncSetAttribute(decode_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
+    if (smem > smem_limit[slot]) return LLMB_ERR_UNSUPPORTED;  // too many layers for the shared-memory table
+    LLMB_CUDA_OK(ensure_dynamic_smem(decode_step_kernel<false>, set_plain, smem));
+    LLMB_CUDA_OK(ensure_dynamic_smem(decode_step_kernel<true>, set_tp, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms);
     cfg.blockDim = dim3(kDsThreads);

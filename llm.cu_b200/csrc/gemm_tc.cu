@@ -425,12 +425,8 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     void (*kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams) =
         dual ? (bn == 128 ? gemm_tc_kernel<true, 128> : bn == 64 ? gemm_tc_kernel<true, 64> : gemm_tc_kernel<true, 32>)
              : (bn == 128 ? gemm_tc_kernel<false, 128> : bn == 64 ? gemm_tc_kernel<false, 64> : gemm_tc_kernel<false, 32>);
-    static size_t attr_set[2][3] = {};
-    size_t &have = attr_set[dual ? 1 : 0][bn == 128 ? 0 : bn == 64 ? 1 : 2];
-    if (smem > have) {
-        LLMB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        have = smem;
-    }
+    static size_t attr_set[2][3][kMaxDevices] = {};  // per instantiation and device
+    LLMB_CUDA_OK(ensure_dynamic_smem(kernel, attr_set[dual ? 1 : 0][bn == 128 ? 0 : bn == 64 ? 1 : 2], smem));
     kernel<<<grid, kGemmThreads, smem, stream>>>(ma, mb, mb2, p);
     LLMB_CUDA_OK(cudaGetLastError());
     return LLMB_OK;

@@ -221,23 +221,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     }
 }
 
-// Development knobs (environment, read once): shared-memory budget per CTA in KB, CTAs per SM,
-// rows per stage for k in (2048, 4096].
-static int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-static const int g_smem_kb = env_int("LLMB_GEMV_SMEM_KB", 100);
-static const int g_ctas_per_sm = env_int("LLMB_GEMV_CTAS", 2);
-static const int g_nr = env_int("LLMB_GEMV_NR", 0);
+// Shared-memory budget of a CTA's weight ring (two CTAs share an SM) and CTAs per SM, from sweeps on B200.
+constexpr int kGemvSmemKb = 100;
+constexpr int kGemvCtasPerSm = 2;
 
 template <int J, int NR, int EPI>
 static int launch_gemv(const GemvParams &p0, int sm_count, bool pdl, cudaStream_t stream) {
     GemvParams p = p0;
     constexpr bool DUAL = (EPI == LLMB_EPI_SWIGLU);
     constexpr int R = DUAL ? NR / 2 : NR;
-    const uint32_t kSmemBudget = (uint32_t)g_smem_kb * 1024;
-    if (J < 8) sm_count *= g_ctas_per_sm;  // the k > 8192 variant needs too many registers for two CTAs per SM
+    const uint32_t kSmemBudget = (uint32_t)kGemvSmemKb * 1024;
+    if (J < 8) sm_count *= kGemvCtasPerSm;  // the k > 8192 variant needs too many registers for two CTAs per SM
     p.stage_bytes = (uint32_t)((size_t)NR * p.k * 2);
     int stages = (int)(kSmemBudget / p.stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
@@ -247,11 +241,8 @@ static int launch_gemv(const GemvParams &p0, int sm_count, bool pdl, cudaStream_
     int grid = p.groups < sm_count ? p.groups : sm_count;
     size_t smem = (size_t)stages * p.stage_bytes;
     auto kern = gemv_kernel<J, NR, EPI>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
-        LLMB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        attr_set = true;
-    }
+    static size_t attr_set[kMaxDevices] = {};  // per instantiation and device
+    LLMB_CUDA_OK(ensure_dynamic_smem(kern, attr_set, kSmemBudget));
     LLMB_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, pdl, p));
     return LLMB_OK;
 }
@@ -260,11 +251,7 @@ template <int EPI>
 static int dispatch_j(const GemvParams &p, int sm_count, bool pdl, cudaStream_t stream) {
     const int chunks = p.k / 8;
     if (chunks <= 256) return launch_gemv<1, 8, EPI>(p, sm_count, pdl, stream);
-    if (chunks <= 512) {
-        if (g_nr == 2) return launch_gemv<2, 2, EPI>(p, sm_count, pdl, stream);
-        if (g_nr == 8) return launch_gemv<2, 8, EPI>(p, sm_count, pdl, stream);
-        return launch_gemv<2, 4, EPI>(p, sm_count, pdl, stream);
-    }
+    if (chunks <= 512) return launch_gemv<2, 4, EPI>(p, sm_count, pdl, stream);
     if (chunks <= 1024) return launch_gemv<4, 2, EPI>(p, sm_count, pdl, stream);
     if constexpr (EPI == LLMB_EPI_STORE || EPI == LLMB_EPI_RESIDUAL) {
         if (chunks <= 2048) return launch_gemv<8, 1, EPI>(p, sm_count, pdl, stream);

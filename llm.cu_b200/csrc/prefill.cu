@@ -288,18 +288,12 @@ extern "C" int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache,
     }
     // two buffers x (K tile + V tile) of 64 padded rows
     const size_t smem = (size_t)4 * kMmaTile * (head_dim + 8) * sizeof(__half);
-    static bool attr_set[2] = {false, false};
+    static size_t attr_set[2][kMaxDevices] = {};  // per instantiation and device
     if (head_dim == 128) {
-        if (!attr_set[0]) {
-            LLMB_CUDA_OK(cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[0] = true;
-        }
+        LLMB_CUDA_OK(ensure_dynamic_smem(attn_prefill_mma_kernel<128>, attr_set[0], smem));
         attn_prefill_mma_kernel<128><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
     } else {
-        if (!attr_set[1]) {
-            LLMB_CUDA_OK(cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[1] = true;
-        }
+        LLMB_CUDA_OK(ensure_dynamic_smem(attn_prefill_mma_kernel<64>, attr_set[1], smem));
         attn_prefill_mma_kernel<64><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
     }
     LLMB_CUDA_OK(cudaGetLastError());

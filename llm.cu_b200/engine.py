@@ -81,6 +81,10 @@ class Cache:
         if step_kernel >= 0:
             check(lib.cache_use_step_kernel(self.ptr, int(step_kernel)), "cache_use_step_kernel")
 
+    def set_tp_poll_limit(self, limit):
+        """Spin limit of the step kernel's waits for tensor-parallel peers (0 = default, about a second)."""
+        check(lib.cache_set_tp_poll_limit(self.ptr, int(limit)), "cache_set_tp_poll_limit")
+
     def set_prefill(self, enable=True, min_rows=0):
         """Prompt tokens as blocks of rows through the tensor-core projections (default), or one by one
         through the decode step; `min_rows` > 0 changes the smallest run that takes the block path."""

@@ -67,6 +67,7 @@ struct Engine {
     void *peers[8] = {};                // every rank's block as mapped on this device
     bool tp_connected = false;
     unsigned long long *trace = nullptr;  // optional per-phase timestamps of the step kernel
+    unsigned int tag_poll_limit = 0;  // spin limit of the step kernel's waits for tensor-parallel peers (0 = default)
     size_t trace_bytes = 0;
     int *h_next = nullptr;  // pinned: [0] next token, [1] device status word
     __half *hidden = nullptr;
@@ -195,7 +196,7 @@ int enqueue_step(Engine *e, bool with_logits, const SplitPlan &sp) {
         lm.epilogue = LLMB_EPI_STORE;
         if ((rc = llmb_gemv_f16(&lm, s))) return rc;
         if ((rc = llmb_argmax_f16(reinterpret_cast<const uint16_t *>(e->logits), e->vocab, e->d_next, e->d_pos,
-                                  e->d_history, e->max_seq, pdl, s)))
+                                  e->d_history, e->max_seq + 1, pdl, s)))
             return rc;
     } else {
         if ((rc = llmb_advance_pos(e->d_pos, pdl, s))) return rc;
@@ -233,7 +234,7 @@ int launch_step_kernel(Engine *e, bool with_logits, int len) {
     a.lm_head = reinterpret_cast<const uint16_t *>(e->model->lm_head->d_fp16_tensor);
     a.g_final = reinterpret_cast<const uint16_t *>(e->model->norm->d_fp16_tensor);
     a.history = e->d_history;
-    a.history_len = e->max_seq;
+    a.history_len = e->max_seq + 1;  // d_history has max_seq + 1 entries: the token sampled at the last row still fits
     a.pos = e->d_pos;
     a.x = reinterpret_cast<uint16_t *>(e->x);
     a.q = reinterpret_cast<uint16_t *>(e->q);
@@ -248,6 +249,7 @@ int launch_step_kernel(Engine *e, bool with_logits, int len) {
     a.with_logits = with_logits ? 1 : 0;
     a.hidden = e->hidden_dump ? reinterpret_cast<uint16_t *>(e->hidden) : nullptr;
     a.trace = reinterpret_cast<uint64_t *>(e->trace);
+    a.tag_poll_limit = e->tag_poll_limit;
     if (e->tp_size > 1) {
         if (!e->tp_connected) {
             set_last_error("tensor parallel cache: call cache_tp_connect() on every rank first");
@@ -638,6 +640,15 @@ extern "C" int cache_reset(CudaCache *cache) {
     // also brings the step kernel's arrival counter back to a known state
     LLMB_CUDA_OK(cudaMemsetAsync(e->step_scratch, 0, e->step_scratch_bytes, e->stream));
     LLMB_CUDA_OK(cudaMemsetAsync(e->attn_scratch, 0, 256, e->stream));
+    // split-K arrival counters of the prompt-phase projections: a launch that wound down early leaves them set
+    if (e->pf_ws) LLMB_CUDA_OK(cudaMemsetAsync(e->pf_ws, 0, 4096, e->stream));
+    return LLMB_OK;
+}
+
+extern "C" int cache_set_tp_poll_limit(CudaCache *cache, unsigned int tag_poll_limit) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    e->tag_poll_limit = tag_poll_limit;
     return LLMB_OK;
 }
 

@@ -51,10 +51,12 @@ def build(force=False):
     return LIB_PATH
 
 
-def build_reference(ref_root="/root/reference"):
-    """Builds oracle/_ref/ref_harness from the reference sources if they are present. Returns the
-    path, or None when the reference tree is absent (the GPU box uses the prebuilt binary)."""
-    if os.path.isdir(os.path.join(ref_root, "src")):
+def build_reference(ref_root=None):
+    """Builds oracle/_ref/ref_harness from the reference sources if they are present. `ref_root` (or the
+    environment variable LLM_CU_REFERENCE) names the reference checkout. Returns the path of the harness,
+    or None when there is neither a checkout nor a prebuilt binary."""
+    ref_root = ref_root or os.environ.get("LLM_CU_REFERENCE", "")
+    if ref_root and os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.run(["make", "-C", HERE, "ref", "REF=" + ref_root], check=True, capture_output=True)
     return REF_HARNESS if os.path.exists(REF_HARNESS) else None
 

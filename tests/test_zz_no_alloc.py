@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 from gpu_util import dev, host_u16  # noqa: E402
 
 
-def run_pair(pkg, oracle, nq, nkv, hd, length, n_splits, split_len, seed):
+def run_pair(pkg, oracle, nq, nkv, hd, length, n_splits, split_len, seed, use_pdl=0, check_free=False):
     max_pos = max(length, 8)
     q = dev(oracle.synth_fp16(seed, 1, nq * hd, std=1.0))
     kc = dev(oracle.synth_fp16(seed, 2, max_pos * nkv * hd, std=1.0))
@@ -26,9 +26,14 @@ def run_pair(pkg, oracle, nq, nkv, hd, length, n_splits, split_len, seed):
     rc = pkg.lib.llmb_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), nq, nkv, hd, n_splits,
                                   split_len, want.data_ptr(), scratch.data_ptr(), 0, None)
     assert rc == 0, pkg.lib.llmb_last_error()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = pkg.lib.llmb_attn_decode_static(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), nq, nkv, hd,
-                                         n_splits, split_len, got.data_ptr(), 0, None)
+                                         n_splits, split_len, got.data_ptr(), use_pdl, None)
     assert rc == 0, pkg.lib.llmb_last_error()
+    torch.cuda.synchronize()
+    if check_free:  # the driver's free-memory figure does not move: the call took nothing from the device
+        assert torch.cuda.mem_get_info()[0] == free_before
     return host_u16(got), host_u16(want)
 
 
@@ -37,11 +42,26 @@ def test_static_workspace_matches_caller_workspace_twice_in_a_row(pkg, oracle):
         pytest.skip("no CUDA device")
     # first call: long sequence, many splits; second call: fewer heads, shorter sequence, so anything
     # the first call left in the shared array would show
-    for args in ((32, 8, 128, 1500, 16, 128, 31), (4, 2, 64, 70, 16, 32, 32)):
-        got, want = run_pair(pkg, oracle, *args)
+    # the third call launches with programmatic stream serialization, as the engine's captured step does
+    calls = (((32, 8, 128, 1500, 16, 128, 31), 0), ((4, 2, 64, 70, 16, 32, 32), 0), ((32, 8, 128, 900, 8, 128, 33), 1))
+    for i, (args, pdl) in enumerate(calls):
+        # the first call on a device may make the CUDA runtime load the library's device code (the array
+        # itself included); from the second call on, free device memory must not change at all
+        got, want = run_pair(pkg, oracle, *args, use_pdl=pdl, check_free=i > 0)
         # same kernel, same split order: the results are identical, well inside the 1-ulp
         # tolerance the attention tests allow against a float64 softmax
         assert np.array_equal(got, want), args
+
+
+def test_static_workspace_on_a_second_device(pkg, oracle):
+    """The array's address and the kernels' shared-memory opt-in are per device: a process that uses two
+    GPUs gets a correct result on both (64 KB of shared memory at head_dim 128 needs the opt-in)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    for d in (0, 1):
+        with torch.cuda.device(d):
+            got, want = run_pair(pkg, oracle, 32, 8, 128, 600, 8, 128, 40 + d)
+            assert np.array_equal(got, want), d
 
 
 def test_static_workspace_rejects_oversized_requests(pkg):
