@@ -130,6 +130,17 @@ int inference(Llama3 *llama3_model, Tensor *X, int *d_tokens, int *h_tokens, Cud
 int llama3_set_config(Llama3 *m, const Llama3Config *cfg); /* fields <= 0 keep their default */
 int llama3_set_tp(Llama3 *m, int tp_rank, int tp_size);
 int llama3_load_safetensors(Llama3 *m, const char *filename);
+/* Loading streams by default: load_safetensor_weights() parses the header and records where each payload
+ * lies; to_cuda() then reads this rank's window of every tensor straight from the file into two pinned
+ * staging buffers (32 MB each) and overlaps the read of one chunk with the upload and BF16 -> FP16
+ * conversion of the previous one, so the host never holds the model.  enable = 0 restores the reference's
+ * behaviour (safetensor.cu:140-155): every payload is read into Tensor::bf16_tensor at load and kept
+ * until to_cuda().  Call before loading. */
+int llama3_set_streaming(Llama3 *m, int enable);
+/* Figures of the last to_cuda(): wall seconds, bytes read from the shard files, bytes copied to the
+ * device, and the pinned host memory it used.  Any pointer may be NULL. */
+int llama3_upload_stats(Llama3 *m, double *seconds, unsigned long long *bytes_read, unsigned long long *bytes_uploaded,
+                        unsigned long long *host_staging_bytes);
 /* The window {row0, rows, col0, cols, full_cols} of a loaded tensor that this model's
  * tensor-parallel rank keeps: q/k/v, gate/up and lm_head split by rows, o_proj and down_proj by
  * columns, everything else whole.  layer = -1, slot 1/2/3 = embed_tokens/lm_head/norm; otherwise
@@ -202,6 +213,22 @@ int cache_set_prefill(CudaCache *cache, int enable, int min_rows);
  * negative status.  The caller appends the token to its array and calls inference() again, as
  * src/main.cu:121-122 does; the engine then feeds just that token. */
 int cache_sample_next_token(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed, uint64_t draw);
+/* Batched decode: n_seqs independent sequences that advance one token per step, the m = n_seqs rows of a
+ * step going through the tensor-core projections so that every weight byte is streamed once per step
+ * (the reference's projections are m-row GEMMs too: inference.cu:393-449).  Each sequence has its own
+ * KV cache of config.max_seq rows: K, V [n_layers][n_seqs][max_seq][n_kv].  Needs tp_size 1.
+ *   cache_batch_init     allocates the batch state (n_seqs <= 128); the single-sequence state is untouched
+ *   cache_batch_prefill  tokens [n_seqs][n_tokens]: all but the last token of every sequence go into its
+ *                        cache as blocks of rows; the last one becomes the input of the next step
+ *   cache_batch_step     one step; tokens (optional [n_seqs]) replaces the inputs (teacher forcing), else the
+ *                        tokens sampled by the previous step are fed; h_logits (optional [n_seqs][vocab] FP16
+ *                        bits) and next_tokens (optional [n_seqs]) receive the step's results
+ *   cache_batch_greedy   n_steps steps with the greedy tokens fed back on the device, no host round trip;
+ *                        out_tokens [n_seqs][n_steps], ms = CUDA-event time of the steps */
+int cache_batch_init(CudaCache *cache, int n_seqs);
+int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_tokens);
+int cache_batch_step(CudaCache *cache, const int *tokens, uint16_t *h_logits, int *next_tokens);
+int cache_batch_greedy(CudaCache *cache, int n_steps, int *out_tokens, float *ms);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

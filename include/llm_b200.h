@@ -141,6 +141,17 @@ int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint1
                      int n_q_heads, int n_kv_heads, int head_dim, int n_splits, int split_len, uint16_t *d_out,
                      void *d_scratch, int use_pdl, llmb_stream_t stream);
 
+/* Batched decode: one new token for each of n_seqs sequences in one launch (grid z = sequence).   */
+/*   q, out   : [n_seqs][n_q_heads * head_dim];  pos : device [n_seqs], position of each new token  */
+/*   k_cache  : [n_seqs][seq_stride_rows][n_kv_heads * head_dim] (this layer), likewise v_cache      */
+/*   n_splits * split_len must cover the longest sequence; scratch as below, counters zero.          */
+/* Replaces compute_attention (inference.cu:698-947) for the last row of each sequence.               */
+size_t llmb_attn_decode_batch_scratch_bytes(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int n_splits);
+int llmb_attn_decode_batch(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                           const int32_t *d_pos, int n_seqs, size_t seq_stride_rows, int n_q_heads, int n_kv_heads,
+                           int head_dim, int n_splits, int split_len, uint16_t *d_out, void *d_scratch, int use_pdl,
+                           llmb_stream_t stream);
+
 /* The same attention for callers that may not allocate device memory (a host whose own pool  */
 /* owns the device, a loop that cannot afford an allocation's synchronisation, a plug-in that  */
 /* only ever sees its input and output buffers): no workspace argument, the partial results     */
@@ -165,6 +176,11 @@ int llmb_attn_decode_static(const uint16_t *d_q, const uint16_t *d_k_cache, cons
 /* ------------------------------------------------------------------------------------ */
 int llmb_argmax_f16(const uint16_t *d_logits, int n, int32_t *d_token_out, int32_t *d_pos_inout,
                     int32_t *d_history, int history_len, int use_pdl, llmb_stream_t stream);
+
+/* The same for `rows` rows of logits ([rows][n], n a multiple of 8), one CTA per row:                 */
+/* token_out[r] = argmax of row r; pos_inout[r]++ (if not NULL); history[r * history_len + pos] = it.   */
+int llmb_argmax_rows_f16(const uint16_t *d_logits, int n, int rows, int32_t *d_token_out, int32_t *d_pos_inout,
+                         int32_t *d_history, int history_len, int use_pdl, llmb_stream_t stream);
 
 /* position += 1 without sampling (prompt rows whose logits nobody reads). */
 int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
@@ -203,6 +219,9 @@ typedef struct {
     size_t workspace_bytes;/* kernel leaves them zero): lets a launch with few output tiles split K across     */
                            /* CTAs; partial sums are added in slice order.  One launch at a time per workspace; */
                            /* 4096 + SMs * 131072 bytes always suffice.                                        */
+    const int32_t *row_pos;/* ROPE_KV, batched decode (one new row per sequence): device [m] cache position of   */
+    int seq_stride;        /* each row; row r then goes to cache row r * seq_stride + row_pos[r] (sequence r of a */
+                           /* [n_seqs][seq_stride][n_kv] cache), and pos0 is ignored.  NULL = rows pos0, pos0+1.. */
 } LlmbGemmArgs;
 
 int llmb_gemm_f16(const LlmbGemmArgs *args, llmb_stream_t stream);

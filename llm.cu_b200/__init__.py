@@ -24,15 +24,16 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_attn_decode_static", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
+    "llmb_attn_decode", "llmb_attn_decode_batch_scratch_bytes", "llmb_attn_decode_batch", "llmb_attn_decode_static", "llmb_argmax_rows_f16", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
     "llmb_rmsnorm_rows", "llmb_attn_prefill", "llmb_iota_i32", "llmb_sample_logits_host", "llmb_sampler_uniform", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
-    "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors",
+    "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors", "llama3_set_streaming", "llama3_upload_stats",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
     "cache_set_options", "cache_use_step_kernel", "cache_set_tp_poll_limit", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
-    "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token",
+    "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token", "cache_batch_init", "cache_batch_prefill",
+    "cache_batch_step", "cache_batch_greedy",
 ]
 
 
@@ -100,6 +101,7 @@ class GemmArgs(C.Structure):
         ("k", C.c_int), ("epilogue", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
         ("rope_cs", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("pos0", C.c_int),
         ("max_pos", C.c_int), ("tile_n", C.c_int), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("row_pos", C.c_void_p), ("seq_stride", C.c_int),
     ]
 
 
@@ -136,6 +138,10 @@ def _declare(l):
     l.llmb_attn_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.llmb_attn_decode_scratch_bytes.restype = sz
     l.llmb_attn_decode.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+    l.llmb_attn_decode_batch_scratch_bytes.argtypes = [i32, i32, i32, i32, i32]
+    l.llmb_attn_decode_batch_scratch_bytes.restype = sz
+    l.llmb_attn_decode_batch.argtypes = [vp, vp, vp, vp, i32, sz, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+    l.llmb_argmax_rows_f16.argtypes = [vp, i32, i32, vp, vp, vp, i32, i32, vp]
     l.llmb_attn_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]
     l.llmb_argmax_f16.argtypes = [vp, i32, vp, vp, vp, i32, i32, vp]
     l.llmb_advance_pos.argtypes = [vp, i32, vp]
@@ -166,6 +172,8 @@ def _declare(l):
     l.llama3_set_tp.argtypes = [M, i32, i32]
     l.llama3_load_safetensors.argtypes = [M, C.c_char_p]
     l.llama3_to_cuda.argtypes = [M]
+    l.llama3_set_streaming.argtypes = [M, i32]
+    l.llama3_upload_stats.argtypes = [M, C.POINTER(C.c_double), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]
     l.llama3_tensor_shard.argtypes = [M, i32, i32, C.POINTER(C.c_int)]
     l.llama3_synth_weights.argtypes = [M, C.POINTER(Llama3Config), u64, i32]
     l.llama3_init_cache.argtypes = [M, C.POINTER(C.c_int)]
@@ -194,6 +202,10 @@ def _declare(l):
     l.cache_set_prefill.argtypes = [K, i32, i32]
     l.cache_sample_next_token.argtypes = [K, C.c_float, i32, C.c_float, u64, u64]
     l.cache_kernel_launches.restype = C.c_longlong
+    l.cache_batch_init.argtypes = [K, i32]
+    l.cache_batch_prefill.argtypes = [K, vp, i32]
+    l.cache_batch_step.argtypes = [K, vp, vp, vp]
+    l.cache_batch_greedy.argtypes = [K, i32, vp, C.POINTER(C.c_float)]
 
 
 lib = None

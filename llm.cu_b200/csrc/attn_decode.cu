@@ -40,6 +40,10 @@ struct AttnParams {
     float *part_ml;  // [n_kv_heads][n_splits][G][2]
     float *part_o;   // [n_kv_heads][n_splits][G][HD]
     int n_kv_heads, n_splits, split_len;
+    // batched decode: blockIdx.z is the sequence; q and out are [n_seqs][n_q], pos is [n_seqs], the caches of
+    // consecutive sequences are seq_stride elements apart (0 for a single sequence)
+    int n_q;
+    size_t seq_stride;
 };
 
 template <int HD, int G>
@@ -58,17 +62,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
     __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x, g = blockIdx.y;
+    const int split = blockIdx.x, g = blockIdx.y, seq = blockIdx.z;
     pdl_launch_dependents();
     pdl_wait();
 
-    const int len_total = *p.pos + 1;
+    const int len_total = p.pos[seq] + 1;
+    const __half *q_seq = p.q + (size_t)seq * p.n_q;
+    const __half *k_seq = p.k_cache + (size_t)seq * p.seq_stride;
+    const __half *v_seq = p.v_cache + (size_t)seq * p.seq_stride;
+    const int gs = seq * p.n_kv_heads + g;  // (sequence, KV head): index of the counter and of the partials
     const int begin = split * p.split_len;
     const int end = min(begin + p.split_len, len_total);
     const size_t row_stride = (size_t)p.n_kv_heads * HD;
     const float inv_den = sqrtf((float)HD);
 
-    for (int i = tid; i < G * HD; i += kAttnThreads) q_s[i] = __half2float(p.q[(size_t)g * G * HD + i]);
+    for (int i = tid; i < G * HD; i += kAttnThreads) q_s[i] = __half2float(q_seq[(size_t)g * G * HD + i]);
 
     float m_run[G], l_run[G], acc[HPT];
 #pragma unroll
@@ -88,8 +96,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
             const int r = c / CHUNKS, ch = c % CHUNKS;
             const int sw = ch ^ (r & 7);
             const size_t goff = (size_t)(t0 + r) * row_stride + (size_t)g * HD + ch * 8;
-            cp_async16(&k_tile[r * HD + sw * 8], p.k_cache + goff);
-            cp_async16(&v_tile[r * HD + ch * 8], p.v_cache + goff);
+            cp_async16(&k_tile[r * HD + sw * 8], k_seq + goff);
+            cp_async16(&v_tile[r * HD + ch * 8], v_seq + goff);
         }
         cp_async_wait_all();
         __syncthreads();
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
         if (lane == 0) red_sum[warp][h] = sm;
     }
     __syncthreads();
-    const size_t pbase = ((size_t)g * p.n_splits + split) * G;
+    const size_t pbase = ((size_t)gs * p.n_splits + split) * G;
     if (tid < G) {
         const float l = (red_sum[0][tid] + red_sum[1][tid]) + (red_sum[2][tid] + red_sum[3][tid]);
         float m = -INFINITY;
@@ -183,9 +191,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const int prev = atomicAdd(&p.counters[g], 1);
+        const int prev = atomicAdd(&p.counters[gs], 1);
         is_last = (prev == p.n_splits - 1);
-        if (is_last) p.counters[g] = 0;  // every split has arrived; ready for the next launch
+        if (is_last) p.counters[gs] = 0;  // every split has arrived; ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
@@ -193,7 +201,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 
     // Merge, in split order.
     const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
-    const size_t gbase = (size_t)g * p.n_splits * G;
+    const size_t gbase = (size_t)gs * p.n_splits * G;
 #pragma unroll
     for (int h = 0; h < HPT; ++h) {
         const int head = my_h0 + h;
@@ -209,16 +217,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
             num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + my_d]), num);
             den = fmaf(wgt, l, den);
         }
-        p.out[((size_t)g * G + head) * HD + my_d] = __float2half_rn(__fdiv_rn(num, den));
+        p.out[(size_t)seq * p.n_q + ((size_t)g * G + head) * HD + my_d] = __float2half_rn(__fdiv_rn(num, den));
     }
 }
 
 template <int HD, int G>
-static int launch_attn(const AttnParams &p, bool pdl, cudaStream_t stream) {
+static int launch_attn(const AttnParams &p, int n_seqs, bool pdl, cudaStream_t stream) {
     constexpr size_t smem = (size_t)2 * kTile * HD * sizeof(__half);
     static size_t attr_set[kMaxDevices] = {};  // per instantiation and device
     LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, smem));
-    LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads), dim3(kAttnThreads), smem,
+    LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads, n_seqs), dim3(kAttnThreads), smem,
                             stream, pdl, p));
     return LLMB_OK;
 }
@@ -234,13 +242,14 @@ extern "C" size_t llmb_attn_decode_scratch_bytes(int n_q_heads, int n_kv_heads, 
     return llmb::attn_counters_bytes(n_kv_heads) + ml + o;
 }
 
-extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
-                                const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
-                                int split_len, uint16_t *d_out, void *d_scratch, int use_pdl, llmb_stream_t stream_) {
+static int attn_decode_impl(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, const int32_t *d_pos,
+                            int n_seqs, size_t seq_stride_elems, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
+                            int split_len, uint16_t *d_out, void *d_scratch, int use_pdl, llmb_stream_t stream_) {
     using namespace llmb;
     if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !d_scratch) return LLMB_ERR_INVALID;
-    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads || n_splits <= 0 || split_len <= 0) return LLMB_ERR_INVALID;
-    if (((uintptr_t)d_scratch & 255) || ((uintptr_t)d_k_cache & 15) || ((uintptr_t)d_v_cache & 15))
+    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads || n_splits <= 0 || split_len <= 0 || n_seqs <= 0 || n_seqs > 65535)
+        return LLMB_ERR_INVALID;
+    if (((uintptr_t)d_scratch & 255) || ((uintptr_t)d_k_cache & 15) || ((uintptr_t)d_v_cache & 15) || (seq_stride_elems & 7))
         return LLMB_ERR_INVALID;
     AttnParams p;
     p.q = reinterpret_cast<const __half *>(d_q);
@@ -248,33 +257,57 @@ extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, 
     p.v_cache = reinterpret_cast<const __half *>(d_v_cache);
     p.pos = d_pos;
     p.out = reinterpret_cast<__half *>(d_out);
+    // scratch of n_seqs sequences = the layout of one sequence with n_seqs times the heads
     unsigned char *sc = static_cast<unsigned char *>(d_scratch);
     p.counters = reinterpret_cast<int *>(sc);
-    sc += attn_counters_bytes(n_kv_heads);
+    sc += attn_counters_bytes(n_kv_heads * n_seqs);
     p.part_ml = reinterpret_cast<float *>(sc);
-    sc += ((size_t)n_q_heads * n_splits * 2 * 4 + 255) / 256 * 256;
+    sc += ((size_t)n_q_heads * n_seqs * n_splits * 2 * 4 + 255) / 256 * 256;
     p.part_o = reinterpret_cast<float *>(sc);
     p.n_kv_heads = n_kv_heads;
     p.n_splits = n_splits;
     p.split_len = split_len;
+    p.n_q = n_q_heads * head_dim;
+    p.seq_stride = seq_stride_elems;
     const int G = n_q_heads / n_kv_heads;
     const bool pdl = use_pdl != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (head_dim == 128) {
         switch (G) {
-            case 1: return launch_attn<128, 1>(p, pdl, stream);
-            case 2: return launch_attn<128, 2>(p, pdl, stream);
-            case 4: return launch_attn<128, 4>(p, pdl, stream);
-            case 8: return launch_attn<128, 8>(p, pdl, stream);
+            case 1: return launch_attn<128, 1>(p, n_seqs, pdl, stream);
+            case 2: return launch_attn<128, 2>(p, n_seqs, pdl, stream);
+            case 4: return launch_attn<128, 4>(p, n_seqs, pdl, stream);
+            case 8: return launch_attn<128, 8>(p, n_seqs, pdl, stream);
         }
     } else if (head_dim == 64) {
         switch (G) {
-            case 2: return launch_attn<64, 2>(p, pdl, stream);
-            case 4: return launch_attn<64, 4>(p, pdl, stream);
-            case 8: return launch_attn<64, 8>(p, pdl, stream);
+            case 2: return launch_attn<64, 2>(p, n_seqs, pdl, stream);
+            case 4: return launch_attn<64, 4>(p, n_seqs, pdl, stream);
+            case 8: return launch_attn<64, 8>(p, n_seqs, pdl, stream);
         }
     }
     return LLMB_ERR_UNSUPPORTED;
+}
+
+extern "C" int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                                const int32_t *d_pos, int n_q_heads, int n_kv_heads, int head_dim, int n_splits,
+                                int split_len, uint16_t *d_out, void *d_scratch, int use_pdl, llmb_stream_t stream_) {
+    return attn_decode_impl(d_q, d_k_cache, d_v_cache, d_pos, 1, 0, n_q_heads, n_kv_heads, head_dim, n_splits, split_len, d_out,
+                            d_scratch, use_pdl, stream_);
+}
+
+extern "C" size_t llmb_attn_decode_batch_scratch_bytes(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int n_splits) {
+    if (n_seqs <= 0) return 0;
+    return llmb_attn_decode_scratch_bytes(n_q_heads * n_seqs, n_kv_heads * n_seqs, head_dim, n_splits);
+}
+
+extern "C" int llmb_attn_decode_batch(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache,
+                                      const int32_t *d_pos, int n_seqs, size_t seq_stride_rows, int n_q_heads, int n_kv_heads,
+                                      int head_dim, int n_splits, int split_len, uint16_t *d_out, void *d_scratch, int use_pdl,
+                                      llmb_stream_t stream_) {
+    if (n_kv_heads <= 0 || head_dim <= 0) return LLMB_ERR_INVALID;
+    return attn_decode_impl(d_q, d_k_cache, d_v_cache, d_pos, n_seqs, seq_stride_rows * (size_t)n_kv_heads * head_dim, n_q_heads,
+                            n_kv_heads, head_dim, n_splits, split_len, d_out, d_scratch, use_pdl, stream_);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -46,6 +46,8 @@ struct GemmParams {
     int *status;
     int M, N, K, epilogue;
     int n_q, n_kv, head_dim, pos0, max_pos;
+    const int *row_pos;  // ROPE_KV, batched decode: cache position of each row; row r belongs to sequence r
+    long long seq_stride;  // cache rows between consecutive sequences
     int stages;  // ring depth of this launch (<= kGemmMaxStages)
     // split-K: blockIdx.z takes a slice of K, partial accumulators meet in the workspace and the last
     // CTA of a tile to arrive adds them in slice order and runs the epilogue
@@ -199,15 +201,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c = 0; c < kBN / 32; ++c) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16) + (uint32_t)(c * 32);
-                tmem_ld32(taddr, v);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    reinterpret_cast<uint4 *>(mine + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (DUAL) {
-                    tmem_ld32(taddr + kBN, v);
+                tmem_ld32(taddr, v);  // warp-collective: every lane takes part, rows past M are not stored
+                if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        reinterpret_cast<uint4 *>(mine + kBN + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        reinterpret_cast<uint4 *>(mine + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+                if (DUAL) {
+                    tmem_ld32(taddr + kBN, v);
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<uint4 *>(mine + kBN + c * 32)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
                 }
             }
             __threadfence();  // this thread's partials are visible device-wide before the arrival is counted
@@ -225,6 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int c = 0; c < kBN / 32 && finish; ++c) {
             uint32_t v[32], u[32];
             if (p.splits > 1) {
+                if (!row_ok) continue;  // no collective below on this path
                 // partial sums in slice order: the result does not depend on which CTA arrived last
                 float fv[32], fu[32];
 #pragma unroll
@@ -280,7 +287,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dst[i] = reinterpret_cast<const uint4 *>(out)[i];
             } else {  // LLMB_EPI_ROPE_KV
-                const int pos = p.pos0 + row;
+                const int pos = p.row_pos ? __ldg(p.row_pos + row) : p.pos0 + row;
+                const size_t cache_row = p.row_pos ? (size_t)row * (size_t)p.seq_stride + (size_t)pos : (size_t)pos;
                 const int half_dim = p.head_dim >> 1;
                 const bool is_v = col0 >= p.n_q + p.n_kv;
 #pragma unroll
@@ -300,8 +308,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 __half *dstp = nullptr;
                 if (col0 < p.n_q) dstp = p.c + (size_t)row * p.n_q + col0;
                 else if (pos >= 0 && pos < p.max_pos)
-                    dstp = (is_v ? p.v_cache + (size_t)pos * p.n_kv + (col0 - p.n_q - p.n_kv)
-                                 : p.k_cache + (size_t)pos * p.n_kv + (col0 - p.n_q));
+                    dstp = (is_v ? p.v_cache + cache_row * p.n_kv + (col0 - p.n_q - p.n_kv)
+                                 : p.k_cache + cache_row * p.n_kv + (col0 - p.n_q));
                 if (dstp) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) reinterpret_cast<uint4 *>(dstp)[i] = reinterpret_cast<const uint4 *>(out)[i];
@@ -402,6 +410,8 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     if (!p.status) return LLMB_ERR_CUDA;
     p.M = a->m; p.N = a->n; p.K = a->k; p.epilogue = a->epilogue;
     p.n_q = a->n_q; p.n_kv = a->n_kv; p.head_dim = a->head_dim; p.pos0 = a->pos0; p.max_pos = a->max_pos;
+    p.row_pos = a->row_pos;
+    p.seq_stride = a->seq_stride;
     dim3 grid(m_tiles, a->n / bn);
     const int tiles = (int)(grid.x * grid.y), k_tiles = a->k / kBK;
     p.splits = 1;

@@ -103,6 +103,11 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __half *__restrict__
     __shared__ int si[32];
     pdl_launch_dependents();
     pdl_wait();
+    // one CTA per row of logits (a single row unless the decode is batched)
+    logits += (size_t)blockIdx.x * n;
+    token_out += blockIdx.x;
+    if (pos_inout) pos_inout += blockIdx.x;
+    if (history) history += (size_t)blockIdx.x * history_len;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     const int n8 = n / 8;
@@ -253,6 +258,16 @@ extern "C" int llmb_argmax_f16(const uint16_t *d_logits, int n, int32_t *d_token
                                int32_t *d_history, int history_len, int use_pdl, llmb_stream_t stream_) {
     if (!d_logits || !d_token_out || n <= 0 || ((uintptr_t)d_logits & 15)) return LLMB_ERR_INVALID;
     LLMB_CUDA_OK(launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream_), use_pdl != 0,
+                            reinterpret_cast<const __half *>(d_logits), n, d_token_out, d_pos_inout, d_history,
+                            history_len));
+    return LLMB_OK;
+}
+
+extern "C" int llmb_argmax_rows_f16(const uint16_t *d_logits, int n, int rows, int32_t *d_token_out, int32_t *d_pos_inout,
+                                    int32_t *d_history, int history_len, int use_pdl, llmb_stream_t stream_) {
+    if (!d_logits || !d_token_out || n <= 0 || rows <= 0 || rows > 65535 || ((uintptr_t)d_logits & 15)) return LLMB_ERR_INVALID;
+    if (rows > 1 && (n % 8)) return LLMB_ERR_UNSUPPORTED;  // every row must start on a 16-byte boundary
+    LLMB_CUDA_OK(launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream_), use_pdl != 0,
                             reinterpret_cast<const __half *>(d_logits), n, d_token_out, d_pos_inout, d_history,
                             history_len));
     return LLMB_OK;

@@ -21,8 +21,10 @@ class Model:
             raise MemoryError("init_llama3 failed")
 
     @classmethod
-    def from_safetensors(cls, cfg, paths, max_seq=2048, tp_rank=0, tp_size=1):
+    def from_safetensors(cls, cfg, paths, max_seq=2048, tp_rank=0, tp_size=1, streaming=True):
         m = cls(cfg.n_layers)
+        if not streaming:
+            check(lib.llama3_set_streaming(m.ptr, 0), "llama3_set_streaming")
         if tp_size > 1:
             check(lib.llama3_set_tp(m.ptr, tp_rank, tp_size), "llama3_set_tp")
         partial = Llama3Config(0, 0, 0, cfg.head_dim, 0, 0, max_seq, cfg.rope_theta, cfg.eps)
@@ -40,6 +42,12 @@ class Model:
         c = _cfg_struct(cfg, max_seq)
         check(lib.llama3_synth_weights(m.ptr, C.byref(c), seed, 1 if cfg.bf16_weights else 0), "llama3_synth_weights")
         return m
+
+    def upload_stats(self):
+        """Figures of the last to_cuda(): seconds, bytes read from files, bytes uploaded, pinned staging bytes."""
+        s, a, b, c = C.c_double(0), C.c_ulonglong(0), C.c_ulonglong(0), C.c_ulonglong(0)
+        check(lib.llama3_upload_stats(self.ptr, C.byref(s), C.byref(a), C.byref(b), C.byref(c)), "llama3_upload_stats")
+        return {"seconds": s.value, "bytes_read": a.value, "bytes_uploaded": b.value, "host_staging_bytes": c.value}
 
     @property
     def config(self):
@@ -158,6 +166,33 @@ class Cache:
         ms = C.c_float(0)
         check(lib.inference_continue(self.model.ptr, self.ptr, n_steps, out, C.byref(ms)), "inference_continue")
         return list(out), ms.value
+
+    # ---- batched decode: n_seqs sequences, one token each per step -------------------------------
+    def batch_init(self, n_seqs):
+        check(lib.cache_batch_init(self.ptr, int(n_seqs)), "cache_batch_init")
+        self.n_seqs = int(n_seqs)
+
+    def batch_prefill(self, prompts):
+        """prompts: [n_seqs][n_tokens] ids; the last token of each stays pending as the next step's input."""
+        a = np.ascontiguousarray(prompts, dtype=np.int32)
+        assert a.ndim == 2 and a.shape[0] == self.n_seqs
+        check(lib.cache_batch_prefill(self.ptr, a.ctypes.data, a.shape[1]), "cache_batch_prefill")
+
+    def batch_step(self, tokens=None, want_logits=True):
+        """One step for every sequence; returns (next tokens [n_seqs], logits uint16 [n_seqs][vocab] or None)."""
+        t = None if tokens is None else np.ascontiguousarray(tokens, dtype=np.int32)
+        lg = np.empty((self.n_seqs, self.vocab), dtype=np.uint16) if want_logits else None
+        nxt = np.empty(self.n_seqs, dtype=np.int32)
+        check(lib.cache_batch_step(self.ptr, None if t is None else t.ctypes.data, None if lg is None else lg.ctypes.data,
+                                   nxt.ctypes.data), "cache_batch_step")
+        return nxt, lg
+
+    def batch_greedy(self, n_steps):
+        """n_steps device-resident greedy steps; returns (tokens [n_seqs][n_steps], ms)."""
+        out = np.empty((self.n_seqs, int(n_steps)), dtype=np.int32)
+        ms = C.c_float(0)
+        check(lib.cache_batch_greedy(self.ptr, int(n_steps), out.ctypes.data, C.byref(ms)), "cache_batch_greedy")
+        return out, ms.value
 
     def kernel_launches(self):
         return lib.cache_kernel_launches(self.ptr)

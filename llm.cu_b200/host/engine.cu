@@ -85,6 +85,15 @@ struct Engine {
     int *pf_pos = nullptr;
     void *pf_ws = nullptr;  // split-K workspace of the projections
     size_t pf_ws_bytes = 0;
+    // batched decode: n_seqs independent sequences advance one token per step
+    int bt_seqs = 0;
+    __half *bt_kcache = nullptr, *bt_vcache = nullptr;  // [layers][n_seqs][max_seq][n_kv]
+    __half *bt_logits = nullptr;                        // [n_seqs][vocab]
+    int *bt_pos = nullptr, *bt_tok = nullptr, *bt_history = nullptr;  // [n_seqs], [n_seqs], [n_seqs][max_seq + 1]
+    void *bt_attn_scratch = nullptr;
+    int bt_max_splits = 0;
+    std::vector<int> bt_len;                            // rows in the cache per sequence (host view)
+    std::map<int, cudaGraphExec_t> bt_graphs;           // key: attention bucket
 };
 
 inline Engine *eng(const CudaCache *c) { return c ? static_cast<Engine *>(c->priv) : nullptr; }
@@ -337,7 +346,9 @@ int ensure_prefill_buffers(Engine *e, int rows) {
 // Appends the K/V rows of history positions [from, to) to the cache, a block of rows at a time:
 // the reference's layer loop (inference.cu:157-186) with every projection a tensor-core GEMM over
 // the block.  No logits: the caller runs the last prompt token through the decode step.
-int prefill_rows(Engine *e, int from, int to) {
+// `ids` = the sequence's token ids on the device (position 0 first); kbase/vbase = layer 0 of the sequence's
+// cache; layer_stride = elements between consecutive layers of that cache.
+int prefill_rows(Engine *e, int from, int to, const int *ids, __half *kbase, __half *vbase, size_t layer_stride) {
     Llama3 *m = e->model;
     const Llama3Config &c = m->config;
     cudaStream_t s = e->stream;
@@ -349,13 +360,13 @@ int prefill_rows(Engine *e, int from, int to) {
     for (int p0 = from; p0 < to; p0 += e->prefill_chunk) {
         const int rows = std::min(e->prefill_chunk, to - p0);
         if ((rc = llmb_iota_i32(e->pf_pos, p0, rows, s))) return rc;
-        if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), e->d_history + p0, e->pf_pos, rows, e->d,
+        if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), ids + p0, e->pf_pos, rows, e->d,
                                   e->embed_rows, e->hd, c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 0, s)))
             return rc;
         for (int l = 0; l < e->layers; ++l) {
             const Llama3Layer *L = m->layers[l];
-            __half *kl = e->kcache + (size_t)l * e->max_seq * n_kv;
-            __half *vl = e->vcache + (size_t)l * e->max_seq * n_kv;
+            __half *kl = kbase + (size_t)l * layer_stride;
+            __half *vl = vbase + (size_t)l * layer_stride;
             if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), rows, e->d,
                                         c.eps, s)))
                 return rc;
@@ -420,7 +431,7 @@ int feed_tokens(Engine *e, const int *ids, int from, int to) {
     int rc, first = from;
     // all but the last token as blocks of rows; the last one through the decode step, for its logits
     if (e->batched_prefill && to - 1 - from >= e->prefill_min_rows && prefill_supported(e)) {
-        if ((rc = prefill_rows(e, from, to - 1))) return rc;
+        if ((rc = prefill_rows(e, from, to - 1, e->d_history, e->kcache, e->vcache, (size_t)e->max_seq * e->nkv * e->hd))) return rc;
         first = to - 1;
     }
     if ((rc = set_device_int(e, e->d_pos, first))) return rc;
@@ -462,6 +473,9 @@ void destroy_engine(Engine *e) {
         if (e->tp_connected && r != e->tp_rank && e->peers[r]) cudaIpcCloseMemHandle(e->peers[r]);
     cudaFree(e->exchange); cudaFree(e->x_alt); cudaFree(e->trace);
     free_prefill_buffers(e);
+    for (auto &kv : e->bt_graphs) cudaGraphExecDestroy(kv.second);
+    cudaFree(e->bt_kcache); cudaFree(e->bt_vcache); cudaFree(e->bt_logits); cudaFree(e->bt_pos); cudaFree(e->bt_tok);
+    cudaFree(e->bt_history); cudaFree(e->bt_attn_scratch);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -903,5 +917,257 @@ extern "C" int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int 
     if ((rc = status_result(e))) return rc;
     if (ms) LLMB_CUDA_OK(cudaEventElapsedTime(ms, e->ev[0], e->ev[1]));
     e->consumed.insert(e->consumed.end(), fed.begin(), fed.end());
+    return LLMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Batched decode: n_seqs independent sequences, one new token each per step.  The reference's
+// projections are written for m rows (kernel_standard_tiled_gemm over all rows, inference.cu:393-449,
+// launched at :561-598 and :950-979); here the m = n_seqs rows of a step go through the tensor-core
+// projections (llmb_gemm_f16), every weight byte is streamed once per step, and each sequence attends
+// over its own cache: K, V [n_layers][n_seqs][max_seq][n_kv].  One step = 2 + 7 * n_layers + 3 kernels,
+// captured once per attention bucket into a CUDA graph.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+SplitPlan plan_batch_splits(int len) {
+    int bucket = 512;
+    while (bucket < len) bucket <<= 1;
+    int split_len = bucket / 8;  // many (sequence, head) pairs fill the GPU already: few, long splits
+    if (split_len < 128) split_len = 128;
+    return {bucket, bucket / split_len, split_len};
+}
+
+int enqueue_batch_step(Engine *e, const SplitPlan &sp) {
+    Llama3 *m = e->model;
+    const Llama3Config &c = m->config;
+    cudaStream_t s = e->stream;
+    const int B = e->bt_seqs;
+    const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    auto u16 = [](const void *p) { return reinterpret_cast<const uint16_t *>(p); };
+    auto u16w = [](void *p) { return reinterpret_cast<uint16_t *>(p); };
+    int rc;
+    if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), e->bt_tok, e->bt_pos, B, e->d, e->embed_rows, e->hd,
+                              c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 0, s)))
+        return rc;
+    const size_t layer_stride = (size_t)B * e->max_seq * n_kv;
+    for (int l = 0; l < e->layers; ++l) {
+        const Llama3Layer *L = m->layers[l];
+        __half *kl = e->bt_kcache + (size_t)l * layer_stride;
+        __half *vl = e->bt_vcache + (size_t)l * layer_stride;
+        if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), B, e->d, c.eps, s)))
+            return rc;
+        LlmbGemmArgs g = {};
+        g.a = u16(e->pf_xn);
+        g.b = u16(L->self_attn_q_proj->d_fp16_tensor);
+        g.c = u16w(e->pf_q);
+        g.m = B; g.n = n_q + 2 * n_kv; g.k = e->d;
+        g.epilogue = LLMB_EPI_ROPE_KV;
+        g.n_q = n_q; g.n_kv = n_kv; g.head_dim = e->hd;
+        g.rope_cs = e->pf_rope;
+        g.k_cache = u16w(kl); g.v_cache = u16w(vl);
+        g.row_pos = e->bt_pos; g.seq_stride = e->max_seq; g.max_pos = e->max_seq;
+        g.workspace = e->pf_ws; g.workspace_bytes = e->pf_ws_bytes;
+        if ((rc = llmb_gemm_f16(&g, s))) return rc;
+        if ((rc = llmb_attn_decode_batch(u16(e->pf_q), u16(kl), u16(vl), e->bt_pos, B, (size_t)e->max_seq, e->nq, e->nkv, e->hd,
+                                         sp.n_splits, sp.split_len, u16w(e->pf_attn), e->bt_attn_scratch, 0, s)))
+            return rc;
+        LlmbGemmArgs o = {};
+        o.a = u16(e->pf_attn);
+        o.b = u16(L->self_attn_o_proj->d_fp16_tensor);
+        o.c = u16w(e->pf_x);
+        o.m = B; o.n = e->d; o.k = n_q;
+        o.epilogue = LLMB_EPI_RESIDUAL;
+        o.workspace = e->pf_ws; o.workspace_bytes = e->pf_ws_bytes;
+        if ((rc = llmb_gemm_f16(&o, s))) return rc;
+        if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->post_attention_layernorm->d_fp16_tensor), u16w(e->pf_xn), B, e->d,
+                                    c.eps, s)))
+            return rc;
+        LlmbGemmArgs f = {};
+        f.a = u16(e->pf_xn);
+        f.b = u16(L->mlp_gate_proj->d_fp16_tensor);
+        f.b2 = u16(L->mlp_up_proj->d_fp16_tensor);
+        f.c = u16w(e->pf_h);
+        f.m = B; f.n = e->ffn; f.k = e->d;
+        f.epilogue = LLMB_EPI_SWIGLU;
+        f.workspace = e->pf_ws; f.workspace_bytes = e->pf_ws_bytes;
+        if ((rc = llmb_gemm_f16(&f, s))) return rc;
+        LlmbGemmArgs dn = {};
+        dn.a = u16(e->pf_h);
+        dn.b = u16(L->mlp_down_proj->d_fp16_tensor);
+        dn.c = u16w(e->pf_x);
+        dn.m = B; dn.n = e->d; dn.k = e->ffn;
+        dn.epilogue = LLMB_EPI_RESIDUAL;
+        dn.workspace = e->pf_ws; dn.workspace_bytes = e->pf_ws_bytes;
+        if ((rc = llmb_gemm_f16(&dn, s))) return rc;
+    }
+    if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(m->norm->d_fp16_tensor), u16w(e->pf_xn), B, e->d, c.eps, s))) return rc;
+    LlmbGemmArgs lm = {};
+    lm.a = u16(e->pf_xn);
+    lm.b = u16(m->lm_head->d_fp16_tensor);
+    lm.c = u16w(e->bt_logits);
+    lm.m = B; lm.n = e->vocab; lm.k = e->d;
+    lm.epilogue = LLMB_EPI_STORE;
+    lm.workspace = e->pf_ws; lm.workspace_bytes = e->pf_ws_bytes;
+    if ((rc = llmb_gemm_f16(&lm, s))) return rc;
+    // greedy token of every sequence -> next step's input; positions advance; history keeps what was sampled
+    return llmb_argmax_rows_f16(u16(e->bt_logits), e->vocab, B, e->bt_tok, e->bt_pos, e->bt_history, e->max_seq + 1, 0, s);
+}
+
+// One batched step for sequences whose longest has `len` rows after it.
+int run_batch_step(Engine *e, int len) {
+    const SplitPlan sp = plan_batch_splits(len);
+    e->launches += 2 + 7 * e->layers + 3;
+    if (!e->use_graph) return enqueue_batch_step(e, sp);
+    auto it = e->bt_graphs.find(sp.bucket);
+    if (it == e->bt_graphs.end()) {
+        cudaGraph_t graph = nullptr;
+        LLMB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        int rc = enqueue_batch_step(e, sp);
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+        if (rc) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        LLMB_CUDA_OK(ce);
+        cudaGraphExec_t exec = nullptr;
+        ce = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        LLMB_CUDA_OK(ce);
+        it = e->bt_graphs.emplace(sp.bucket, exec).first;
+    }
+    LLMB_CUDA_OK(cudaGraphLaunch(it->second, e->stream));
+    return LLMB_OK;
+}
+
+bool batch_supported(const Engine *e) {
+    return prefill_supported(e) && e->vocab % 128 == 0;
+}
+
+}  // namespace
+
+extern "C" int cache_batch_init(CudaCache *cache, int n_seqs) {
+    Engine *e = eng(cache);
+    if (!e || n_seqs < 1 || n_seqs > 128) return LLMB_ERR_INVALID;
+    if (!batch_supported(e)) {
+        set_last_error("cache_batch_init: batched decode needs the whole model on this GPU (tp_size 1), head_dim 64 or 128 and "
+                       "projection widths (q+k+v, d_model, ffn, vocab) that are multiples of 128");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    for (auto &kv : e->bt_graphs) cudaGraphExecDestroy(kv.second);
+    e->bt_graphs.clear();
+    cudaFree(e->bt_kcache); cudaFree(e->bt_vcache); cudaFree(e->bt_logits); cudaFree(e->bt_pos); cudaFree(e->bt_tok);
+    cudaFree(e->bt_history); cudaFree(e->bt_attn_scratch);
+    e->bt_kcache = e->bt_vcache = e->bt_logits = nullptr;
+    e->bt_pos = e->bt_tok = e->bt_history = nullptr;
+    e->bt_attn_scratch = nullptr;
+    e->bt_seqs = 0;
+    const size_t n_kv = (size_t)e->nkv * e->hd;
+    const size_t kv_bytes = (size_t)e->layers * n_seqs * e->max_seq * n_kv * 2;
+    e->bt_max_splits = plan_batch_splits(e->max_seq).n_splits;
+    const size_t scratch = llmb_attn_decode_batch_scratch_bytes(n_seqs, e->nq, e->nkv, e->hd, e->bt_max_splits);
+    cudaError_t ce = cudaSuccess;
+    auto alloc = [&](void **p, size_t bytes) {
+        if (ce == cudaSuccess) ce = cudaMalloc(p, bytes);
+        if (ce == cudaSuccess) ce = cudaMemsetAsync(*p, 0, bytes, e->stream);
+    };
+    alloc(reinterpret_cast<void **>(&e->bt_kcache), kv_bytes);
+    alloc(reinterpret_cast<void **>(&e->bt_vcache), kv_bytes);
+    alloc(reinterpret_cast<void **>(&e->bt_logits), (size_t)n_seqs * e->vocab * 2);
+    alloc(reinterpret_cast<void **>(&e->bt_pos), sizeof(int) * (size_t)n_seqs);
+    alloc(reinterpret_cast<void **>(&e->bt_tok), sizeof(int) * (size_t)n_seqs);
+    alloc(reinterpret_cast<void **>(&e->bt_history), sizeof(int) * (size_t)n_seqs * (e->max_seq + 1));
+    alloc(&e->bt_attn_scratch, scratch);
+    if (ce != cudaSuccess) return cuda_fail(ce, __FILE__, __LINE__);
+    int rc = ensure_prefill_buffers(e, std::max(n_seqs, e->prefill_chunk));
+    if (rc) return rc;
+    e->bt_seqs = n_seqs;
+    e->bt_len.assign((size_t)n_seqs, 0);
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    return LLMB_OK;
+}
+
+// tokens: [n_seqs][n_tokens] host ids.  All but the last token of every sequence go through the block
+// path into that sequence's cache; the last one is left as the input of the next cache_batch_step().
+extern "C" int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_tokens) {
+    Engine *e = eng(cache);
+    if (!e || !tokens || e->bt_seqs < 1 || n_tokens < 1) return LLMB_ERR_INVALID;
+    if (n_tokens > e->max_seq) {
+        set_last_error("cache_batch_prefill: prompt longer than config.max_seq");
+        return LLMB_ERR_INVALID;
+    }
+    const int B = e->bt_seqs;
+    const size_t n_kv = (size_t)e->nkv * e->hd;
+    std::vector<int> last((size_t)B), pos((size_t)B, n_tokens - 1);
+    int rc;
+    for (int b = 0; b < B; ++b) {
+        int *hist = e->bt_history + (size_t)b * (e->max_seq + 1);
+        LLMB_CUDA_OK(cudaMemcpyAsync(hist, tokens + (size_t)b * n_tokens, sizeof(int) * (size_t)n_tokens, cudaMemcpyHostToDevice,
+                                     e->stream));
+        if (n_tokens > 1 &&
+            (rc = prefill_rows(e, 0, n_tokens - 1, hist, e->bt_kcache + (size_t)b * e->max_seq * n_kv,
+                               e->bt_vcache + (size_t)b * e->max_seq * n_kv, (size_t)B * e->max_seq * n_kv)))
+            return rc;
+        last[(size_t)b] = tokens[(size_t)b * n_tokens + n_tokens - 1];
+    }
+    LLMB_CUDA_OK(cudaMemcpyAsync(e->bt_tok, last.data(), sizeof(int) * (size_t)B, cudaMemcpyHostToDevice, e->stream));
+    LLMB_CUDA_OK(cudaMemcpyAsync(e->bt_pos, pos.data(), sizeof(int) * (size_t)B, cudaMemcpyHostToDevice, e->stream));
+    if ((rc = queue_status_read(e))) return rc;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));  // `last` and `pos` are stack-lifetime host buffers
+    if ((rc = status_result(e))) return rc;
+    e->bt_len.assign((size_t)B, n_tokens - 1);
+    return LLMB_OK;
+}
+
+// One batched step.  tokens (optional, [n_seqs]): the input token of every sequence (teacher forcing); NULL
+// feeds what the previous step sampled (or the last prompt token after cache_batch_prefill).  h_logits
+// (optional, [n_seqs][vocab] FP16 bits) and next_tokens (optional, [n_seqs]) are copied back when given.
+extern "C" int cache_batch_step(CudaCache *cache, const int *tokens, uint16_t *h_logits, int *next_tokens) {
+    Engine *e = eng(cache);
+    if (!e || e->bt_seqs < 1) return LLMB_ERR_INVALID;
+    const int B = e->bt_seqs;
+    const int len = e->bt_len[0] + 1;
+    if (len > e->max_seq) {
+        set_last_error("cache_batch_step: would run past config.max_seq");
+        return LLMB_ERR_INVALID;
+    }
+    if (tokens) LLMB_CUDA_OK(cudaMemcpyAsync(e->bt_tok, tokens, sizeof(int) * (size_t)B, cudaMemcpyHostToDevice, e->stream));
+    int rc = run_batch_step(e, len);
+    if (rc) return rc;
+    if (h_logits)
+        LLMB_CUDA_OK(cudaMemcpyAsync(h_logits, e->bt_logits, (size_t)B * e->vocab * 2, cudaMemcpyDeviceToHost, e->stream));
+    if (next_tokens)
+        LLMB_CUDA_OK(cudaMemcpyAsync(next_tokens, e->bt_tok, sizeof(int) * (size_t)B, cudaMemcpyDeviceToHost, e->stream));
+    if ((rc = queue_status_read(e))) return rc;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if ((rc = status_result(e))) return rc;
+    for (int &l : e->bt_len) l += 1;
+    return LLMB_OK;
+}
+
+// n_steps greedy steps with the sampled tokens fed back on the device; out_tokens [n_seqs][n_steps].
+extern "C" int cache_batch_greedy(CudaCache *cache, int n_steps, int *out_tokens, float *ms) {
+    Engine *e = eng(cache);
+    if (!e || e->bt_seqs < 1 || n_steps < 1 || !out_tokens) return LLMB_ERR_INVALID;
+    const int B = e->bt_seqs, start = e->bt_len[0];
+    if (start + n_steps > e->max_seq) {
+        set_last_error("cache_batch_greedy: would run past config.max_seq");
+        return LLMB_ERR_INVALID;
+    }
+    int rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[0], e->stream));
+    for (int i = 0; i < n_steps; ++i)
+        if ((rc = run_batch_step(e, start + i + 1))) return rc;
+    LLMB_CUDA_OK(cudaEventRecord(e->ev[1], e->stream));
+    // the token sampled by the step at position p sits at history[p + 1]
+    LLMB_CUDA_OK(cudaMemcpy2DAsync(out_tokens, sizeof(int) * (size_t)n_steps, e->bt_history + start + 1,
+                                   sizeof(int) * (size_t)(e->max_seq + 1), sizeof(int) * (size_t)n_steps, (size_t)B,
+                                   cudaMemcpyDeviceToHost, e->stream));
+    if ((rc = queue_status_read(e))) return rc;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    if ((rc = status_result(e))) return rc;
+    if (ms) LLMB_CUDA_OK(cudaEventElapsedTime(ms, e->ev[0], e->ev[1]));
+    for (int &l : e->bt_len) l += n_steps;
     return LLMB_OK;
 }

@@ -8,8 +8,17 @@
 //     the fused QKV projection streams a single contiguous span; the three Tensor structs keep
 //     valid row-major views into it (k and v are marked device_is_view);
 //   * every other tensor has its own 256-byte-aligned allocation;
-//   * one reusable staging buffer carries the BF16 payload to the device (the reference
-//     cudaMallocs and frees a staging buffer per tensor, llama3.cu:203, :234).
+//   * to_cuda streams: this rank's window of every tensor is read straight from its shard file (pread)
+//     into one of two pinned staging buffers in chunks of rows, copied to the device with
+//     cudaMemcpyAsync and converted BF16 -> FP16 on the same stream, while the host already reads the
+//     next chunk into the other buffer.  The host holds two staging buffers, never the model (the
+//     reference reads every tensor whole into host memory at load, safetensor.cu:140-155, and
+//     cudaMallocs and frees a device staging buffer per tensor, llama3.cu:203, :234).
+#include <fcntl.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -23,6 +32,30 @@
 using namespace llmb;
 
 static Tensor *new_tensor() { return static_cast<Tensor *>(calloc(1, sizeof(Tensor))); }
+
+ModelPriv *llmb::model_priv(Llama3 *m) {
+    if (!m) return nullptr;
+    if (!m->priv) m->priv = new (std::nothrow) ModelPriv();
+    return static_cast<ModelPriv *>(m->priv);
+}
+
+extern "C" int llama3_set_streaming(Llama3 *m, int enable) {
+    ModelPriv *pv = model_priv(m);
+    if (!pv) return LLMB_ERR_INVALID;
+    pv->streaming = enable != 0;
+    return LLMB_OK;
+}
+
+extern "C" int llama3_upload_stats(Llama3 *m, double *seconds, unsigned long long *bytes_read,
+                                   unsigned long long *bytes_uploaded, unsigned long long *host_staging_bytes) {
+    ModelPriv *pv = model_priv(m);
+    if (!pv) return LLMB_ERR_INVALID;
+    if (seconds) *seconds = pv->upload_seconds;
+    if (bytes_read) *bytes_read = pv->bytes_read;
+    if (bytes_uploaded) *bytes_uploaded = pv->bytes_uploaded;
+    if (host_staging_bytes) *host_staging_bytes = pv->staging_bytes;
+    return LLMB_OK;
+}
 
 extern "C" Llama3 *init_llama3(int n_layers) {
     if (n_layers <= 0) return nullptr;
@@ -122,6 +155,7 @@ extern "C" void free_llama3(Llama3 *m) {
         }
         free(m->layers);
     }
+    delete static_cast<ModelPriv *>(m->priv);
     free(m);
 }
 
@@ -326,49 +360,151 @@ static void set_local_shape(Tensor *t, const Shard &s) {
     *t->mem_len = (int)s.elems();
 }
 
+namespace {
+
+// Two pinned host buffers and two device buffers that take turns: while chunk i is on its way to the device
+// (and being converted there), the host fills the other buffer with chunk i + 1.
+struct UploadPipe {
+    static constexpr size_t kChunkBytes = (size_t)32 << 20;
+    void *pinned[2] = {nullptr, nullptr};
+    void *dev[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaStream_t stream = nullptr;
+    size_t capacity = 0;
+    int turn = 0;
+    std::vector<int> fds;
+
+    int open(size_t max_row_bytes, bool need_dev) {
+        capacity = std::max(kChunkBytes, max_row_bytes);
+        LLMB_CUDA_OK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            LLMB_CUDA_OK(cudaMallocHost(&pinned[i], capacity));
+            if (need_dev) LLMB_CUDA_OK(cudaMalloc(&dev[i], capacity));
+            LLMB_CUDA_OK(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+        }
+        return LLMB_OK;
+    }
+    ~UploadPipe() {
+        if (stream) cudaStreamSynchronize(stream);
+        for (int i = 0; i < 2; ++i) {
+            if (pinned[i]) cudaFreeHost(pinned[i]);
+            if (dev[i]) cudaFree(dev[i]);
+            if (done[i]) cudaEventDestroy(done[i]);
+        }
+        if (stream) cudaStreamDestroy(stream);
+        for (int fd : fds)
+            if (fd >= 0) close(fd);
+    }
+};
+
+bool pread_all(int fd, void *dst, size_t bytes, unsigned long long offset) {
+    unsigned char *p = static_cast<unsigned char *>(dst);
+    while (bytes > 0) {
+        const ssize_t got = pread(fd, p, bytes, (off_t)offset);
+        if (got <= 0) return false;
+        p += got;
+        bytes -= (size_t)got;
+        offset += (unsigned long long)got;
+    }
+    return true;
+}
+
+}  // namespace
+
 extern "C" int llama3_to_cuda(Llama3 *m) {
     if (!m) return LLMB_ERR_INVALID;
     int rc = derive_config(m);
     if (rc) return rc;
     if ((rc = check_tp(m))) return rc;
     if ((rc = place_tensors(m))) return rc;
+    ModelPriv *pv = model_priv(m);
+    if (!pv) return LLMB_ERR_NOMEM;
+    const auto t_start = std::chrono::steady_clock::now();
     const int rank = m->tp_rank, size = m->tp_size;
-    size_t max_elems = 0;
+    size_t max_row_bytes = 0;
+    bool any_bf16 = false;
     for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
-        const size_t n = shard_of(t, layer, slot, rank, size).elems();
-        if (n > max_elems) max_elems = n;
+        max_row_bytes = std::max(max_row_bytes, (size_t)shard_of(t, layer, slot, rank, size).cols * 2);
+        any_bf16 = any_bf16 || t->file_dtype != 1;
     });
-    void *staging = nullptr;
-    LLMB_CUDA_OK(cudaMalloc(&staging, max_elems * 2));
+    UploadPipe pipe;
+    if ((rc = pipe.open(max_row_bytes, any_bf16))) return rc;
+    pipe.fds.assign(pv->files.size(), -1);
+    pv->bytes_read = pv->bytes_uploaded = 0;
+    pv->staging_bytes = 2ull * pipe.capacity;
     int status = LLMB_OK;
     for_each_tensor(m, [&](Tensor *t, int layer, int slot) {
         if (status) return;
-        if (!t->bf16_tensor) {
-            set_last_error("to_cuda: tensor payload missing on the host");
+        const auto src_it = pv->sources.find(t);
+        const bool from_file = !t->bf16_tensor && src_it != pv->sources.end();
+        if (!t->bf16_tensor && !from_file) {
+            set_last_error("to_cuda: tensor payload missing (neither in host memory nor in a loaded shard)");
             status = LLMB_ERR_INVALID;
             return;
         }
-        const Shard sh = shard_of(t, layer, slot, rank, size);
-        const size_t n = sh.elems();
-        // this rank's window of the host tensor: rows [row0, row0 + rows), columns [col0, col0 + cols)
-        const uint16_t *src = t->bf16_tensor + (size_t)sh.row0 * sh.full_cols + sh.col0;
-        void *dst = (t->file_dtype == 1) ? static_cast<void *>(t->d_fp16_tensor) : staging;
-        cudaError_t e = cudaMemcpy2D(dst, (size_t)sh.cols * 2, src, (size_t)sh.full_cols * 2, (size_t)sh.cols * 2,
-                                     (size_t)sh.rows, cudaMemcpyHostToDevice);
-        if (t->file_dtype != 1) {  // BF16 file: convert on the device (F16 files pass through)
-            if (e == cudaSuccess) {
-                int r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(staging),
-                                          reinterpret_cast<uint16_t *>(t->d_fp16_tensor), n, nullptr);
-                if (r) status = r;
-                if (!r) e = cudaDeviceSynchronize();  // staging is reused by the next tensor
+        int fd = -1;
+        if (from_file) {
+            const int fi = src_it->second.file;
+            if (pipe.fds[(size_t)fi] < 0) pipe.fds[(size_t)fi] = ::open(pv->files[(size_t)fi].c_str(), O_RDONLY);
+            fd = pipe.fds[(size_t)fi];
+            if (fd < 0) {
+                set_last_error(("to_cuda: cannot reopen " + pv->files[(size_t)fi]).c_str());
+                status = LLMB_ERR_IO;
+                return;
             }
         }
-        if (e != cudaSuccess && !status) status = cuda_fail(e, __FILE__, __LINE__);
+        const Shard sh = shard_of(t, layer, slot, rank, size);
+        const size_t row_bytes = (size_t)sh.cols * 2, full_row_bytes = (size_t)sh.full_cols * 2;
+        const int chunk_rows = (int)std::max<size_t>(1, pipe.capacity / row_bytes);
+        uint16_t *dst = reinterpret_cast<uint16_t *>(t->d_fp16_tensor);
+        for (int r0 = 0; r0 < sh.rows && !status; r0 += chunk_rows) {
+            const int nr = std::min(chunk_rows, sh.rows - r0);
+            const size_t bytes = (size_t)nr * row_bytes;
+            const int b = pipe.turn & 1;
+            cudaError_t e = cudaEventSynchronize(pipe.done[b]);  // the copy that last used this buffer has left the host
+            unsigned char *stage = static_cast<unsigned char *>(pipe.pinned[b]);
+            // this rank's window: rows [row0 + r0, + nr), columns [col0, col0 + cols)
+            const size_t first = ((size_t)(sh.row0 + r0) * sh.full_cols + sh.col0) * 2;
+            bool ok = true;
+            if (from_file) {
+                if (sh.cols == sh.full_cols) {
+                    ok = pread_all(fd, stage, bytes, src_it->second.offset + first);
+                } else {
+                    for (int i = 0; i < nr && ok; ++i)
+                        ok = pread_all(fd, stage + (size_t)i * row_bytes, row_bytes, src_it->second.offset + first + (size_t)i * full_row_bytes);
+                }
+                pv->bytes_read += bytes;
+            } else {
+                const unsigned char *base = reinterpret_cast<const unsigned char *>(t->bf16_tensor) + first;
+                for (int i = 0; i < nr; ++i) memcpy(stage + (size_t)i * row_bytes, base + (size_t)i * full_row_bytes, row_bytes);
+            }
+            if (!ok) {
+                set_last_error("to_cuda: short read from a shard file (changed or truncated since it was loaded?)");
+                status = LLMB_ERR_IO;
+                break;
+            }
+            uint16_t *out = dst + (size_t)r0 * sh.cols;
+            if (t->file_dtype == 1) {  // F16 files pass through
+                if (e == cudaSuccess) e = cudaMemcpyAsync(out, stage, bytes, cudaMemcpyHostToDevice, pipe.stream);
+            } else {                   // BF16: convert on the device (llama3.cu:240-254)
+                if (e == cudaSuccess) e = cudaMemcpyAsync(pipe.dev[b], stage, bytes, cudaMemcpyHostToDevice, pipe.stream);
+                if (e == cudaSuccess) {
+                    const int r = llmb_bf16_to_fp16(static_cast<const uint16_t *>(pipe.dev[b]), out, bytes / 2, pipe.stream);
+                    if (r) status = r;
+                }
+            }
+            if (e == cudaSuccess) e = cudaEventRecord(pipe.done[b], pipe.stream);
+            if (e != cudaSuccess && !status) status = cuda_fail(e, __FILE__, __LINE__);
+            pv->bytes_uploaded += bytes;
+            ++pipe.turn;
+        }
         free(t->bf16_tensor);  // llama3.cu:211
         t->bf16_tensor = nullptr;
         set_local_shape(t, sh);
     });
-    cudaFree(staging);
+    cudaError_t e = cudaStreamSynchronize(pipe.stream);
+    if (e != cudaSuccess && !status) status = cuda_fail(e, __FILE__, __LINE__);
+    pv->upload_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count();
     return status;
 }
 

@@ -11,6 +11,11 @@
 // "data_offsets"; anything else, e.g. "__metadata__", is skipped).  Unlike the reference it
 // checks dtype (BF16 is converted at upload, F16 passes through, anything else is an error),
 // payload size against shape, offsets against the file size, and the layer index.
+//
+// By default the loader only records where each payload lies (file, offset): to_cuda then reads
+// this rank's window of every tensor straight from the file into pinned staging buffers, so the host
+// never holds more than those buffers.  With llama3_set_streaming(m, 0) the payload is read here
+// into Tensor::bf16_tensor, as the reference does (safetensor.cu:140-155), and kept until to_cuda.
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -19,6 +24,7 @@
 #include <vector>
 
 #include "../../include/llama3.h"
+#include "host_internal.h"
 
 namespace llmb {
 void set_last_error(const char *msg);
@@ -251,6 +257,9 @@ extern "C" int llama3_load_safetensors(Llama3 *m, const char *filename) {
         return fail(LLMB_ERR_IO, "%s: Error parsing JSON", filename);
 
     const unsigned long long data_base = 8ull + header_size;
+    llmb::ModelPriv *priv = llmb::model_priv(m);
+    if (!priv) return fail(LLMB_ERR_NOMEM, "load_safetensor_weights: out of memory");
+    int file_index = -1;
     for (const Entry &e : entries) {
         int needs_layer = 0;
         Tensor *t = slot_of_key(m, e.name, &needs_layer);
@@ -278,20 +287,33 @@ extern "C" int llama3_load_safetensors(Llama3 *m, const char *filename) {
                         e.name.c_str());
 
         free(t->ndim); free(t->mem_len); free(t->shape); free(t->bf16_tensor);
+        t->bf16_tensor = nullptr;
         t->ndim = static_cast<int *>(malloc(sizeof(int)));
         t->mem_len = static_cast<int *>(malloc(sizeof(int)));
         t->shape = static_cast<int *>(malloc(sizeof(int) * 2));
-        t->bf16_tensor = static_cast<uint16_t *>(malloc((size_t)count * 2));
-        if (!t->ndim || !t->mem_len || !t->shape || !t->bf16_tensor)
+        if (!t->ndim || !t->mem_len || !t->shape)
             return fail(LLMB_ERR_NOMEM, "Error: An Error Occurred while allocating memory for the component Tensor");
         *t->ndim = (int)e.shape.size();
         t->shape[0] = (int)e.shape[0];
         t->shape[1] = e.shape.size() > 1 ? (int)e.shape[1] : 1;
         *t->mem_len = (int)count;
         t->file_dtype = dtype;
-        if (fseek(fp, (long)(data_base + e.begin), SEEK_SET) != 0 ||
-            fread(t->bf16_tensor, 2, (size_t)count, fp) != (size_t)count)
-            return fail(LLMB_ERR_IO, "%s: short read on '%s'", filename, e.name.c_str());
+        if (file_index < 0) {
+            priv->files.push_back(filename);
+            file_index = (int)priv->files.size() - 1;
+        }
+        llmb::TensorSource src;
+        src.file = file_index;
+        src.offset = data_base + e.begin;
+        priv->sources[t] = src;
+        if (!priv->streaming) {
+            t->bf16_tensor = static_cast<uint16_t *>(malloc((size_t)count * 2));
+            if (!t->bf16_tensor)
+                return fail(LLMB_ERR_NOMEM, "Error: An Error Occurred while allocating memory for the component Tensor");
+            if (fseek(fp, (long)(data_base + e.begin), SEEK_SET) != 0 ||
+                fread(t->bf16_tensor, 2, (size_t)count, fp) != (size_t)count)
+                return fail(LLMB_ERR_IO, "%s: short read on '%s'", filename, e.name.c_str());
+        }
         t->loaded = 1;
     }
     return LLMB_OK;

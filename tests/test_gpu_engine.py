@@ -77,6 +77,30 @@ def test_tiny_graph_pdl_and_plain_paths_agree_bitwise(pkg, oracle, tiny_weights)
     model.close()
 
 
+def test_streaming_and_eager_load_give_the_same_model(pkg, oracle, tmp_path):
+    """BF16 checkpoint through both loader modes: streaming (windows read from the file into two pinned staging
+    buffers at to_cuda) and eager (the reference's: every payload in host memory between load and to_cuda)."""
+    from dataclasses import replace
+    cfg = replace(pkg.CONFIGS["tiny"], name="tiny_bf16", bf16_weights=True)
+    w = oracle.Weights(cfg, seed=5)
+    shard = w.write_safetensors(tmp_path / "model.safetensors")
+    tokens = oracle.synth_tokens(5, 18, cfg.vocab)
+    outs = []
+    for streaming in (True, False):
+        m = pkg.Model.from_safetensors(cfg, [shard], max_seq=64, streaming=streaming)
+        st = m.upload_stats()
+        model_bytes = 2 * (cfg.matmul_params() + 2 * cfg.vocab * cfg.d_model + (2 * cfg.n_layers + 1) * cfg.d_model)
+        assert st["bytes_uploaded"] == model_bytes, st
+        assert st["bytes_read"] == (model_bytes if streaming else 0)
+        assert st["host_staging_bytes"] == 2 * (32 << 20) and st["seconds"] > 0
+        cache = pkg.Cache(m)
+        toks = [cache.infer(tokens[:n]) for n in (16, 17, 18)]
+        outs.append((toks, cache.logits()))
+        cache.close()
+        m.close()
+    assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1])
+
+
 def test_tiny_safetensors_load_path_matches_synthetic(pkg, oracle, tiny_weights, tmp_path):
     cfg = pkg.CONFIGS["tiny"]
     names = list(tiny_weights.file)

@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, cfg_name, n_prompt, n_steps, result_path):
+def _rank_main(rank, world, port, cfg_name, n_prompt, n_steps, result_path, shard_path=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -32,7 +32,16 @@ def _rank_main(rank, world, port, cfg_name, n_prompt, n_steps, result_path):
     cfg = pkg.CONFIGS[cfg_name]
     vocab_ids = cfg.embed_rows or cfg.vocab
     tokens = oracle.synth_tokens(0, n_prompt + n_steps, vocab_ids)
-    model = pkg.Model.synthetic(cfg, seed=0, max_seq=256, tp_rank=rank, tp_size=world)
+    if shard_path:
+        # the streaming loader under tensor parallelism: every rank reads only its windows of the shard file
+        # (whole rows for q/k/v, gate/up, lm_head; a slice of every row for o_proj and down_proj)
+        model = pkg.Model.from_safetensors(cfg, [shard_path], max_seq=256, tp_rank=rank, tp_size=world)
+        st = model.upload_stats()
+        assert st["bytes_read"] == st["bytes_uploaded"] and st["host_staging_bytes"] <= 2 * (32 << 20)
+        full = 2 * (cfg.matmul_params() + 2 * cfg.vocab * cfg.d_model)
+        assert st["bytes_read"] < 0.8 * full, st   # a rank does not read the other rank's shards
+    else:
+        model = pkg.Model.synthetic(cfg, seed=0, max_seq=256, tp_rank=rank, tp_size=world)
     cache = pkg.Cache(model)
     cache.tp_connect()
     ok, worst = True, 0.0
@@ -89,4 +98,17 @@ def test_tensor_parallel_decode_matches_oracle(cfg_name, world, tmp_path):
     mp.spawn(_rank_main, args=(world, _free_port(), cfg_name, 16, 6, str(result)), nprocs=world, join=True)
     status, worst, toks = result.read_text().split(" ", 2)
     print("TP=%d %s: worst |dlogit| %s, greedy %s" % (world, cfg_name, worst, toks))
+    assert status == "1", "worst |dlogit| %s" % worst
+
+
+def test_tensor_parallel_streaming_load_from_a_shard_file(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from conftest import load_package
+    from oracle import oracle_lib as oracle
+    pkg = load_package()
+    shard = oracle.Weights(pkg.CONFIGS["tiny"], seed=0).write_safetensors(str(tmp_path / "model.safetensors"))
+    result = tmp_path / "r.txt"
+    mp.spawn(_rank_main, args=(2, _free_port(), "tiny", 16, 6, str(result), shard), nprocs=2, join=True)
+    status, worst, toks = result.read_text().split(" ", 2)
     assert status == "1", "worst |dlogit| %s" % worst

@@ -24,6 +24,7 @@ def test_load_maps_every_key_to_its_slot(pkg, oracle, tiny_weights, tmp_path):
     p1 = tiny_weights.write_safetensors(tmp_path / "a.safetensors", names[: len(names) // 2])
     p2 = tiny_weights.write_safetensors(tmp_path / "b.safetensors", names[len(names) // 2:])
     m = pkg.lib.init_llama3(cfg.n_layers)
+    assert pkg.lib.llama3_set_streaming(m, 0) == 0   # keep the payloads in host memory, as the reference does
     for p in (p1, p2):
         assert pkg.lib.llama3_load_safetensors(m, str(p).encode()) == 0, pkg.lib.llmb_last_error()
     mc = m.contents
@@ -52,6 +53,7 @@ def write_raw(path, header, payload=b"", header_len=None):
 @pytest.fixture
 def model(pkg):
     m = pkg.lib.init_llama3(2)
+    pkg.lib.llama3_set_streaming(m, 0)
     yield m
     pkg.lib.free_llama3(m)
 
@@ -127,3 +129,20 @@ def test_tp_arguments(pkg, model):
     assert pkg.lib.llama3_set_tp(model, 7, 8) == 0
     assert pkg.lib.llama3_set_tp(model, 2, 2) == pkg.ERR_INVALID
     assert pkg.lib.llama3_set_tp(model, 0, 16) == pkg.ERR_UNSUPPORTED
+
+
+def test_streaming_load_keeps_no_payload_on_the_host(pkg, oracle, tiny_weights, tmp_path):
+    """Default mode: the loader records where each payload lies (shape, dtype, file offset) and leaves
+    Tensor::bf16_tensor empty; to_cuda() later reads the windows it needs straight from the file."""
+    cfg = pkg.CONFIGS["tiny"]
+    path = tiny_weights.write_safetensors(tmp_path / "all.safetensors")
+    m = pkg.lib.init_llama3(cfg.n_layers)
+    assert pkg.lib.llama3_load_safetensors(m, str(path).encode()) == 0, pkg.lib.llmb_last_error()
+    t = m.contents.lm_head.contents
+    assert not t.bf16_tensor and t.loaded == 1
+    assert [t.shape[0], t.shape[1]] == [cfg.vocab, cfg.d_model] and t.mem_len[0] == cfg.vocab * cfg.d_model
+    lay = m.contents.layers[1].contents
+    assert not lay.mlp_down_proj.contents.bf16_tensor and lay.mlp_down_proj.contents.shape[1] == cfg.ffn
+    out = (C.c_int * 5)()
+    assert pkg.lib.llama3_tensor_shard(m, 1, 1, out) == 0 and list(out) == [0, cfg.d_model, 0, cfg.ffn, cfg.ffn]
+    pkg.lib.free_llama3(m)

@@ -27,6 +27,7 @@ def _rank_main(rank, world, port, shard_path, result_path):
     pkg = load_package()
     cfg = pkg.CONFIGS["tiny"]
     m = pkg.lib.init_llama3(cfg.n_layers)
+    pkg.lib.llama3_set_streaming(m, 0)   # the test slices the payloads held in host memory
     assert pkg.lib.llama3_set_tp(m, rank, world) == 0
     assert pkg.lib.llama3_load_safetensors(m, shard_path.encode()) == 0
     weights = oracle.Weights(cfg, seed=0)
