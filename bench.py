@@ -315,7 +315,7 @@ def run_ours(args):
                  "roofline": {"bound": "hbm", "achieved": bach, "peak": hbm_peak, "unit": "GB/s", "frac": bach / hbm_peak,
                               "algorithmic_bytes_per_step": bbytes,
                               "scope": "one batched step = weights once + every sequence's KV rows; %d launches per step "
-                                       "in a CUDA graph" % (2 + 7 * cfg.n_layers + 3)},
+                                       "in a CUDA graph" % (2 + 7 * cfg.n_layers + 2)},
                  "path": "tcgen05 projections at m = n_seqs rows, split-KV decode attention per sequence, per-row argmax"}
 
     times = torch.tensor([ms / 1e3, e2e_s], dtype=torch.float64, device="cuda")
@@ -404,6 +404,10 @@ def run_reference(args):
         return
     from oracle import oracle_lib as oracle
     cfg = load_configs()[args.config]
+    if (cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab) != (4096, 32, 8, 128, 14336, 128256):
+        print(json.dumps(dict(base, unavailable="the reference's dimensions are literals of the 8B shape (inference.cu:212-220, "
+                                                ":700, :752, :799); it cannot run %s" % cfg.name)))
+        return
     steps = min(args.steps, args.ref_max_steps)
     warm = min(max(args.warmup, 1), 2)
     need = cfg.weight_bytes_per_token() + (1 << 30)

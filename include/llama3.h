@@ -213,6 +213,12 @@ int cache_set_prefill(CudaCache *cache, int enable, int min_rows);
  * negative status.  The caller appends the token to its array and calls inference() again, as
  * src/main.cu:121-122 does; the engine then feeds just that token. */
 int cache_sample_next_token(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed, uint64_t draw);
+/* The same sampling done by one kernel on the device logits (llmb_sample_logits): nothing but the 4-byte
+ * token crosses to the host, so inference() can run with copy_logits off.  The token also replaces the
+ * greedy one in the device history (inference_continue() then continues from it).  Returns the token, or a
+ * negative status: -LLMB_ERR_UNSUPPORTED when top_k (after clamping to the vocabulary) exceeds 1024 or the
+ * top-p prefix runs past 1024 entries; cache_sample_next_token() takes such a step. */
+int cache_sample_next_token_device(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed, uint64_t draw);
 /* Batched decode: n_seqs independent sequences that advance one token per step, the m = n_seqs rows of a
  * step going through the tensor-core projections so that every weight byte is streamed once per step
  * (the reference's projections are m-row GEMMs too: inference.cu:393-449).  Each sequence has its own
@@ -226,6 +232,8 @@ int cache_sample_next_token(CudaCache *cache, float temperature, int top_k, floa
  *   cache_batch_greedy   n_steps steps with the greedy tokens fed back on the device, no host round trip;
  *                        out_tokens [n_seqs][n_steps], ms = CUDA-event time of the steps */
 int cache_batch_init(CudaCache *cache, int n_seqs);
+/* Cache rows per attention CTA of the batched step (a power of two, 32..512; default 256). */
+int cache_batch_set_split_len(CudaCache *cache, int split_len);
 int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_tokens);
 int cache_batch_step(CudaCache *cache, const int *tokens, uint16_t *h_logits, int *next_tokens);
 int cache_batch_greedy(CudaCache *cache, int n_steps, int *out_tokens, float *ms);

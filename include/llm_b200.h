@@ -95,7 +95,7 @@ int llmb_embed_rope(const uint16_t *d_embed, const int32_t *d_tokens, const int3
 /*                             = kernel_standard_tiled_gemm_ffn_swiglu (inference.cu:455)   */
 /* ------------------------------------------------------------------------------------ */
 enum { LLMB_PRO_NONE = 0, LLMB_PRO_RMSNORM = 1 };
-enum { LLMB_EPI_STORE = 0, LLMB_EPI_RESIDUAL = 1, LLMB_EPI_ROPE_KV = 2, LLMB_EPI_SWIGLU = 3 };
+enum { LLMB_EPI_STORE = 0, LLMB_EPI_RESIDUAL = 1, LLMB_EPI_ROPE_KV = 2, LLMB_EPI_SWIGLU = 3, LLMB_EPI_TP_SCATTER = 4 };
 
 typedef struct {
     const uint16_t *w;     /* [n][k] FP16 */
@@ -199,7 +199,9 @@ int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
 /*                      k, v -> cache row pos0 + row                     (inference.cu:640-695) */
 /*   LLMB_EPI_SWIGLU    c = half(SiLU(A.b^T) * (A.b2^T)), accumulators not rounded  (:515)     */
 /* n must be a multiple of 128, k of 64; a, b, c 16-byte aligned; m is free (rows past m are   */
-/* zero-filled on load and never stored).                                                     */
+/* zero-filled on load and never stored).  With m <= 32 (and tile_n 0) the launch is a weight  */
+/* stream: the weight tile is the 128-row MMA operand, the m rows the 32-column one, K is split */
+/* until two CTAs per SM stream weights (workspace as below), bound by HBM like llmb_gemv_f16.  */
 /* ------------------------------------------------------------------------------------ */
 typedef struct {
     const uint16_t *a;     /* [m][k] FP16 activations */
@@ -222,9 +224,45 @@ typedef struct {
     const int32_t *row_pos;/* ROPE_KV, batched decode (one new row per sequence): device [m] cache position of   */
     int seq_stride;        /* each row; row r then goes to cache row r * seq_stride + row_pos[r] (sequence r of a */
                            /* [n_seqs][seq_stride][n_kv] cache), and pos0 is ignored.  NULL = rows pos0, pos0+1.. */
+    int use_pdl;           /* m <= 32 only: launch with programmatic stream serialization; the kernel then starts  */
+                           /* its weight stream while the previous kernel of the stream is still finishing and     */
+                           /* waits for it (griddepcontrol.wait) before it reads a or writes anything              */
+    /* LLMB_EPI_TP_SCATTER (m <= 32 only): tensor parallel, row-parallel projection (o_proj, down_proj: this rank  */
+    /* holds a slice of K).  The FP32 partial sums are not stored in c: every element goes, as an 8-byte           */
+    /* (value, tag) pair, straight into every rank's exchange block over NVLink (peer stores), where                */
+    /* llmb_tp_gather_rows adds the ranks' partials.  tp_peers[r] = rank r's block as mapped on this device;         */
+    /* tp_index = number of this exchange within the step (selects one of two receive buffers and the tag).         */
+    void *tp_peers[8];
+    int tp_rank, tp_size, tp_index;
+    uint64_t *trace;       /* optional profiling aid (m <= 32 only): device [CTAs][8] nanosecond stamps per CTA (entry,  */
+                           /* set up, previous kernel complete, first stage landed, last MMA issued, accumulators        */
+                           /* complete, partials published, epilogue done); CTA index = slice * tiles + tile.  NULL in   */
+                           /* production.                                                                                */
 } LlmbGemmArgs;
 
 int llmb_gemm_f16(const LlmbGemmArgs *args, llmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Tensor parallel, rows at once (m <= 32): the other half of the all-reduce that                */
+/* LLMB_EPI_TP_SCATTER starts, fused with the residual add and the next RMSNorm.  One CTA per     */
+/* row: polls (bounded) the tp_size tagged partial sums of every element in this rank's exchange  */
+/* block, adds them in rank order (every rank gets the same bits),                                 */
+/*   x[r][c] = half(float(half(sum)) + float(x[r][c]))     (inference.cu:445, :377-390)            */
+/* and, if gamma != NULL, xn = RMSNorm(x) * gamma with the reference's reduction order              */
+/* (inference.cu:293-363).  exchange = this rank's block of llmb_decode_step_exchange_bytes() bytes. */
+/* llmb_tp_argmax_rows: the greedy token of every row from the ranks' vocabulary slices: local      */
+/* first maximum, exchanged through tagged slots, every rank picks the same winner; pos and        */
+/* history advance as in llmb_argmax_rows_f16.  llmb_tp_advance ends a step: the exchange counter   */
+/* moves on by n_exchanges (2 * n_layers, + 1 if llmb_tp_argmax_rows ran).                          */
+/* Replaces the NCCL all-reduce a tensor-parallel port of the reference would place after o_proj    */
+/* and down_proj.                                                                                  */
+/* ------------------------------------------------------------------------------------ */
+int llmb_tp_gather_rows(void *d_exchange, int tp_size, int tp_index, uint16_t *d_x, const uint16_t *d_gamma, uint16_t *d_xn,
+                        int m, int d, double eps, uint32_t poll_limit, int use_pdl, llmb_stream_t stream);
+int llmb_tp_argmax_rows(void *const *d_peers, int tp_rank, int tp_size, int d_model, int tp_index, const uint16_t *d_logits,
+                        int n_local, int vocab_offset, int rows, int32_t *d_token_out, int32_t *d_pos_inout,
+                        int32_t *d_history, int history_len, uint32_t poll_limit, int use_pdl, llmb_stream_t stream);
+int llmb_tp_advance(void *d_exchange, int tp_size, int d_model, int n_exchanges, int use_pdl, llmb_stream_t stream);
 
 /* RMSNorm of m rows of d FP16 values: y = half(x * gamma / rms(x)), the reduction order and  */
 /* rounding of kernel_compute_rms_norm / kernel_compute_norm_tensor (inference.cu:272-375).    */
@@ -261,6 +299,21 @@ int llmb_iota_i32(int32_t *d_out, int first, int n, llmb_stream_t stream);
 int llmb_sample_logits_host(const uint16_t *h_logits_fp16, int vocab, float temperature, int top_k, float top_p,
                             float u, int32_t *token_out);
 float llmb_sampler_uniform(uint64_t seed, uint64_t draw);
+
+/* The same chain on the device, over the FP16 logits a decode step left in device memory: one      */
+/* kernel, no copy of the logits to the host.  u = llmb_sampler_uniform(seed, draw).  The sum of the */
+/* t_i is a tree over threads and expf is CUDA's, so probabilities can differ from the host code's  */
+/* by a few FP32 ulps; the token differs only if u lies that close to a boundary.  Orders at most    */
+/* 1024 entries: top_k (after clamping to vocab) above that returns LLMB_ERR_UNSUPPORTED.            */
+/*   scratch   : llmb_sample_scratch_bytes(vocab) bytes, 256-byte aligned; its first int32 is the     */
+/*               result code of the last call: 0 ok, 1 expf overflow, 2 the top-p prefix ran past    */
+/*               1024 entries (token_out is -1 in both cases: use the host sampler for that step)    */
+/*   token_out : the sampled id; if pos and history are given, history[*pos] = id as well (the       */
+/*               position the decode step has already advanced to: the next step then feeds it)     */
+size_t llmb_sample_scratch_bytes(int vocab);
+int llmb_sample_logits(const uint16_t *d_logits, int vocab, float temperature, int top_k, float top_p, uint64_t seed,
+                       uint64_t draw, void *d_scratch, int32_t *d_token_out, int32_t *d_pos, int32_t *d_history,
+                       int history_len, int use_pdl, llmb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------ */
 /* One whole decode step as a single persistent kernel: every phase of the reference's     */

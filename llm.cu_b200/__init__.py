@@ -18,21 +18,21 @@ LIB_PATH = os.path.join(_HERE, "libllm_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_IO, ERR_NOMEM = range(7)
 PRO_NONE, PRO_RMSNORM = 0, 1
-EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU = 0, 1, 2, 3
+EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU, EPI_TP_SCATTER = 0, 1, 2, 3, 4
 
 # Symbols include/llm_b200.h and include/llama3.h declare; tests check each is exported.
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
     "llmb_attn_decode", "llmb_attn_decode_batch_scratch_bytes", "llmb_attn_decode_batch", "llmb_attn_decode_static", "llmb_argmax_rows_f16", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
-    "llmb_rmsnorm_rows", "llmb_attn_prefill", "llmb_iota_i32", "llmb_sample_logits_host", "llmb_sampler_uniform", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
+    "llmb_rmsnorm_rows", "llmb_tp_gather_rows", "llmb_tp_argmax_rows", "llmb_tp_advance", "llmb_attn_prefill", "llmb_iota_i32", "llmb_sample_logits_host", "llmb_sampler_uniform", "llmb_sample_scratch_bytes", "llmb_sample_logits", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
     "init_llama3", "free_llama3", "_free_tensor", "load_safetensor_weights", "to_cuda", "init_cache",
     "tokens_to_cuda", "inference", "llama3_set_config", "llama3_set_tp", "llama3_load_safetensors", "llama3_set_streaming", "llama3_upload_stats",
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
     "cache_set_options", "cache_use_step_kernel", "cache_set_tp_poll_limit", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
-    "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token", "cache_batch_init", "cache_batch_prefill",
+    "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token", "cache_sample_next_token_device", "cache_batch_init", "cache_batch_set_split_len", "cache_batch_prefill",
     "cache_batch_step", "cache_batch_greedy",
 ]
 
@@ -101,7 +101,9 @@ class GemmArgs(C.Structure):
         ("k", C.c_int), ("epilogue", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
         ("rope_cs", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("pos0", C.c_int),
         ("max_pos", C.c_int), ("tile_n", C.c_int), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("row_pos", C.c_void_p), ("seq_stride", C.c_int),
+        ("row_pos", C.c_void_p), ("seq_stride", C.c_int), ("use_pdl", C.c_int),
+        ("tp_peers", C.c_void_p * 8), ("tp_rank", C.c_int), ("tp_size", C.c_int), ("tp_index", C.c_int),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -147,10 +149,16 @@ def _declare(l):
     l.llmb_advance_pos.argtypes = [vp, i32, vp]
     l.llmb_gemm_f16.argtypes = [C.POINTER(GemmArgs), vp]
     l.llmb_rmsnorm_rows.argtypes = [vp, vp, vp, i32, i32, C.c_double, vp]
+    l.llmb_tp_gather_rows.argtypes = [vp, i32, i32, vp, vp, vp, i32, i32, C.c_double, C.c_uint32, i32, vp]
+    l.llmb_tp_argmax_rows.argtypes = [vp, i32, i32, i32, i32, vp, i32, i32, i32, vp, vp, vp, i32, C.c_uint32, i32, vp]
+    l.llmb_tp_advance.argtypes = [vp, i32, i32, i32, i32, vp]
     l.llmb_attn_prefill.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
     l.llmb_iota_i32.argtypes = [vp, i32, i32, vp]
     l.llmb_sample_logits_host.argtypes = [vp, i32, C.c_float, i32, C.c_float, C.c_float, C.POINTER(C.c_int32)]
     l.llmb_sampler_uniform.argtypes = [u64, u64]
+    l.llmb_sample_scratch_bytes.argtypes = [i32]
+    l.llmb_sample_scratch_bytes.restype = sz
+    l.llmb_sample_logits.argtypes = [vp, i32, C.c_float, i32, C.c_float, u64, u64, vp, vp, vp, vp, i32, i32, vp]
     l.llmb_sampler_uniform.restype = C.c_float
     M, K = C.POINTER(Llama3Struct), C.POINTER(CudaCacheStruct)
     l.init_llama3.argtypes = [i32]
@@ -201,8 +209,10 @@ def _declare(l):
     l.cache_kernel_launches.argtypes = [K]
     l.cache_set_prefill.argtypes = [K, i32, i32]
     l.cache_sample_next_token.argtypes = [K, C.c_float, i32, C.c_float, u64, u64]
+    l.cache_sample_next_token_device.argtypes = [K, C.c_float, i32, C.c_float, u64, u64]
     l.cache_kernel_launches.restype = C.c_longlong
     l.cache_batch_init.argtypes = [K, i32]
+    l.cache_batch_set_split_len.argtypes = [K, i32]
     l.cache_batch_prefill.argtypes = [K, vp, i32]
     l.cache_batch_step.argtypes = [K, vp, vp, vp]
     l.cache_batch_greedy.argtypes = [K, i32, vp, C.POINTER(C.c_float)]

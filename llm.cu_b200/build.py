@@ -18,7 +18,10 @@ SOURCES = [
     "csrc/attn_decode.cu",
     "csrc/decode_step.cu",
     "csrc/gemm_tc.cu",
+    "csrc/gemm_smallm.cu",
     "csrc/prefill.cu",
+    "csrc/sampler.cu",
+    "csrc/tp_rows.cu",
     "host/model.cu",
     "host/engine.cu",
     "host/safetensor.cpp",
@@ -27,6 +30,8 @@ SOURCES = [
 HEADERS = [
     "csrc/common.cuh",
     "csrc/gemv_common.cuh",
+    "csrc/gemm_common.cuh",
+    "csrc/tp_common.cuh",
     "host/host_internal.h",
     "../include/llm_b200.h",
     "../include/llama3.h",

@@ -57,4 +57,7 @@ CONFIGS = {
     # 8B layer shape cut down to ~2.3 GB (4 layers, 32K vocabulary) for multi-pass profiler captures
     "llama3_8b_prof": ModelConfig("llama3_8b_prof", 4, 4096, 32, 8, 128, 14336, 32768),
     "llama3_70b": ModelConfig("llama3_70b", 80, 8192, 64, 8, 128, 28672, 128256),
+    # 70B layer shape, two layers, small embedding table: the parity case of the 70B shape (the CPU oracle runs
+    # it in seconds; under tensor parallelism each of 8 GPUs holds one KV head and 8 query heads)
+    "llama3_70b_l2": ModelConfig("llama3_70b_l2", 2, 8192, 64, 8, 128, 28672, 128256, embed_rows=1024),
 }

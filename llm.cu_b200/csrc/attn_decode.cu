@@ -9,8 +9,9 @@
 //   grid   (n_splits, n_kv_heads); CTA (s, g) handles cache rows [s*split_len, (s+1)*split_len)
 //          of KV head g for all `G` query heads of that group, so K and V are read once per
 //          group, not once per query head.
-//   block  128 threads.  Scores: thread t owns cache row t of the tile and computes the G dot
-//          products in FP32 ascending d, the order of the reference (inference.cu:776-778),
+//   block  128 threads; tiles of 64 cache rows, two buffers: the next tile streams in (cp.async)
+//          while this one is used.  Scores: thread t < 64 owns cache row t of the tile and computes
+//          the G dot products in FP32 ascending d, the order of the reference (inference.cu:776-778),
 //          from a 16-byte-chunk XOR-swizzled shared-memory tile (conflict-free row reads).
 //          P.V: thread t owns output dimension t % head_dim.
 //   merge  each CTA writes (max, sum, unnormalised out) per query head to scratch; the last
@@ -23,7 +24,7 @@
 namespace llmb {
 
 constexpr int kAttnThreads = 128;
-constexpr int kTile = 128;
+constexpr int kTile = 64;  // cache rows per shared-memory tile; two tiles take turns (one streams in while the other is used)
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -53,8 +54,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
     constexpr int HPT = G / DGROUPS;            // query heads per thread in the P.V phase
     static_assert(G % DGROUPS == 0 && HPT >= 1, "group size must fill the block");
     extern __shared__ __align__(128) unsigned char attn_smem[];
-    __half *k_tile = reinterpret_cast<__half *>(attn_smem);
-    __half *v_tile = k_tile + kTile * HD;
+    // two buffers of (K tile, V tile); a split of at most one tile needs only the first
+    const int tile_rows = min(kTile, p.split_len);
     __shared__ __align__(16) float q_s[G * HD];
     __shared__ __align__(16) float p_s[kTile * G];
     __shared__ float red_max[4][G];
@@ -89,18 +90,36 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
     const int my_d = tid % HD;
     const int my_h0 = (DGROUPS == 1) ? 0 : (tid / HD) * HPT;
 
-    for (int t0 = begin; t0 < end; t0 += kTile) {
-        const int rows = min(kTile, end - t0);
-        __syncthreads();  // previous tile fully consumed (also publishes q_s)
+    // Requests tile i of this split into buffer i & 1 (one cp.async group per tile and thread).
+    auto request_tile = [&](int i) {
+        const int t0 = begin + i * kTile, rows = min(kTile, end - t0);
+        __half *kd = reinterpret_cast<__half *>(attn_smem) + (size_t)(i & 1) * 2 * tile_rows * HD;
+        __half *vd = kd + tile_rows * HD;
         for (int c = tid; c < rows * CHUNKS; c += kAttnThreads) {
             const int r = c / CHUNKS, ch = c % CHUNKS;
             const int sw = ch ^ (r & 7);
             const size_t goff = (size_t)(t0 + r) * row_stride + (size_t)g * HD + ch * 8;
-            cp_async16(&k_tile[r * HD + sw * 8], k_seq + goff);
-            cp_async16(&v_tile[r * HD + ch * 8], v_seq + goff);
+            cp_async16(&kd[r * HD + sw * 8], k_seq + goff);
+            cp_async16(&vd[r * HD + ch * 8], v_seq + goff);
         }
-        cp_async_wait_all();
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = end > begin ? (end - begin + kTile - 1) / kTile : 0;
+    if (n_tiles > 0) request_tile(0);
+    for (int ti = 0; ti < n_tiles; ++ti) {
+        const int t0 = begin + ti * kTile;
+        const int rows = min(kTile, end - t0);
+        // the next tile streams in while this one is used (its buffer was released by the barrier that ended
+        // the previous iteration)
+        if (ti + 1 < n_tiles) {
+            request_tile(ti + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // every thread's pieces of this tile have landed (also publishes q_s)
+        const __half *k_tile = reinterpret_cast<const __half *>(attn_smem) + (size_t)(ti & 1) * 2 * tile_rows * HD;
+        const __half *v_tile = k_tile + tile_rows * HD;
 
         // scores for cache row t0 + tid
         float s[G];
@@ -155,7 +174,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
             m_run[h] = m_new;
             float pv = active ? expf(s[h] - m_new) : 0.0f;
             l_run[h] = l_run[h] * scale[h] + pv;  // per-thread partial of the softmax denominator
-            p_s[tid * G + h] = pv;
+            if (tid < kTile) p_s[tid * G + h] = pv;   // threads past the tile hold no row
         }
         __syncthreads();
         // P.V for this tile
@@ -166,6 +185,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 #pragma unroll
             for (int h = 0; h < HPT; ++h) acc[h] = fmaf(p_s[r * G + my_h0 + h], vf, acc[h]);
         }
+        __syncthreads();  // this tile's buffer and p_s are free for the tile after next
     }
 
     // CTA totals: denominators across threads, then publish the partial.
@@ -223,9 +243,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 
 template <int HD, int G>
 static int launch_attn(const AttnParams &p, int n_seqs, bool pdl, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)2 * kTile * HD * sizeof(__half);
+    // (K tile, V tile) of min(64, split_len) rows, twice if the split has more than one tile
+    const size_t smem = (size_t)(p.split_len > kTile ? 2 : 1) * 2 * (p.split_len < kTile ? p.split_len : kTile) * HD * sizeof(__half);
     static size_t attr_set[kMaxDevices] = {};  // per instantiation and device
-    LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, smem));
+    LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, (size_t)4 * kTile * HD * sizeof(__half)));
     LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads, n_seqs), dim3(kAttnThreads), smem,
                             stream, pdl, p));
     return LLMB_OK;

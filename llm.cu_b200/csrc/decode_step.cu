@@ -35,6 +35,7 @@
 #include <cstdlib>
 
 #include "gemv_common.cuh"
+#include "tp_common.cuh"
 
 namespace llmb {
 
@@ -80,23 +81,6 @@ struct DsParams {
     __half *x_alt;              // second residual-stream buffer (ping-pong across all-reduces)
     unsigned char *peer[8];     // every rank's exchange block (own block at [tp_rank]); see TpBlock
 };
-
-// Layout of a rank's exchange block, written by its peers over NVLink:
-//   [0, 64)      flags[r]  u64: highest synchronisation number rank r has announced
-//   [128, 136)   this rank's own count of synchronisations so far (local, persists across launches)
-//   [256, 512)   best[r]   (float value, int index): rank r's best logit of this step
-//   [136, 144)   this rank's count of all-reduces so far (the tag base; local, persists)
-//   [512, ...)   recv[2][tp_size][d_model] of (FP32 partial sum, 32-bit tag): double-buffered.  A value
-//                and its tag travel in one 8-byte store, and a reader spins until the tag is the number
-//                of the all-reduce it is performing, so no fence, flag or barrier stands between a
-//                projection and the all-reduced row (the low-latency protocol of collective libraries).
-//   then         row[2][d_model / 2] of (two FP16 values, 32-bit tag): the all-reduced residual row,
-//                written only by this rank.  Each 16-byte chunk of the row has one owner CTA, which
-//                alone polls the tp_size partial sums, adds them in rank order and publishes the chunk
-//                here with the same tag; every other CTA polls d_model * 4 local bytes instead of
-//                tp_size * d_model * 8 bytes of partial sums.
-constexpr size_t kTpFlagsOff = 0, kTpBestOff = 256, kTpRecvOff = 512;
-__host__ __device__ constexpr size_t tp_row_off(int tp_size, int d) { return kTpRecvOff + (size_t)2 * tp_size * d * 8; }
 
 enum { PH_QKV = 0, PH_O = 1, PH_GU = 2, PH_DOWN = 3, PH_LM = 4 };
 
@@ -973,7 +957,7 @@ static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 extern "C" size_t llmb_decode_step_exchange_bytes(int tp_size, int d_model) {
     if (tp_size < 1 || d_model <= 0) return 0;
-    return tp_row_off(tp_size, d_model) + (size_t)2 * d_model * 4;
+    return tp_exchange_bytes(tp_size, d_model);  // both parts: the whole-step kernel's and the row-batched path's
 }
 
 extern "C" size_t llmb_decode_step_scratch_bytes(int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {

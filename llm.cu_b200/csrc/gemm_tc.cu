@@ -23,80 +23,9 @@
 // A launch with few output tiles and a caller-provided workspace splits K over blockIdx.z: partial
 // accumulators are written to the workspace in FP32, and the last CTA of a tile to arrive adds them in
 // slice order and runs the epilogue.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace llmb {
-
-constexpr int kBM = 128, kBK = 64;
-constexpr int kGemmThreads = 192;
-constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 16 KB: the A tile of a stage
-constexpr int kGemmMaxStages = 8;
-// Ring depth: two CTAs share an SM when the grid has more CTAs than SMs (3 stages each, 2 for SwiGLU);
-// a grid that leaves every CTA alone on its SM gets a ring as deep as shared memory allows, because
-// then the copy latency is hidden by nothing but the ring.
-__host__ __device__ constexpr int gemm_stages(bool dual) { return dual ? 2 : 3; }
-__host__ __device__ constexpr uint32_t gemm_stage_bytes(bool dual, int bn) { return kATileBytes + (dual ? 2 : 1) * bn * kBK * 2; }
-
-struct GemmParams {
-    __half *c;              // STORE/RESIDUAL/SWIGLU: [M][N] (SWIGLU: N = ffn); ROPE_KV: q [M][n_q]
-    const float2 *rope_cs;  // ROPE_KV: [M][head_dim / 2]
-    __half *k_cache, *v_cache;
-    int *status;
-    int M, N, K, epilogue;
-    int n_q, n_kv, head_dim, pos0, max_pos;
-    const int *row_pos;  // ROPE_KV, batched decode: cache position of each row; row r belongs to sequence r
-    long long seq_stride;  // cache rows between consecutive sequences
-    int stages;  // ring depth of this launch (<= kGemmMaxStages)
-    // split-K: blockIdx.z takes a slice of K, partial accumulators meet in the workspace and the last
-    // CTA of a tile to arrive adds them in slice order and runs the epilogue
-    int splits;
-    float *ws_part;  // [tiles][splits][128][accumulator columns]
-    int *ws_count;   // [tiles], zero between launches
-};
-
-__device__ __forceinline__ uint64_t umma_desc(const void *smem_tile) {
-    // K-major, 128-byte swizzle: rows are 128 bytes, 8-row groups are 1024 bytes apart (SBO);
-    // descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
-    const uint64_t addr = smem_u32(smem_tile);
-    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ float silu_gemm(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
 
 template <bool DUAL, int kBN>
 __global__ void __launch_bounds__(kGemmThreads, 2)
@@ -342,7 +271,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 // [rows][k] FP16 row-major as a 2-D tensor map with a 64 x box_rows box and 128-byte swizzle.
-static int make_map(CUtensorMap *map, const void *base, int rows, int k, int box_rows) {
+int make_map(CUtensorMap *map, const void *base, int rows, int k, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_last_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -366,9 +295,16 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int k, int box
 
 extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
     using namespace llmb;
-    if (!a || !a->a || !a->b || !a->c || a->m <= 0 || a->n <= 0 || a->k <= 0) return LLMB_ERR_INVALID;
-    if (a->n % 128 || a->k % kBK) {
+    if (!a || !a->a || !a->b || (!a->c && a->epilogue != LLMB_EPI_TP_SCATTER) || a->m <= 0 || a->n <= 0 || a->k <= 0) return LLMB_ERR_INVALID;
+    const bool small_m = a->m <= 32 && a->tile_n == 0;
+    // the weight-streaming kernel masks the tail of its last tile, so STORE / TP_SCATTER take any n there
+    const bool any_n = small_m && (a->epilogue == LLMB_EPI_STORE || a->epilogue == LLMB_EPI_TP_SCATTER) && a->n % 8 == 0;
+    if ((a->n % 128 && !any_n) || a->k % kBK) {
         set_last_error("llmb_gemm_f16: n must be a multiple of 128 and k a multiple of 64");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    if (a->epilogue == LLMB_EPI_TP_SCATTER && !small_m) {
+        set_last_error("llmb_gemm_f16: LLMB_EPI_TP_SCATTER needs m <= 32");
         return LLMB_ERR_UNSUPPORTED;
     }
     const bool dual = a->epilogue == LLMB_EPI_SWIGLU;
@@ -377,9 +313,11 @@ extern "C" int llmb_gemm_f16(const LlmbGemmArgs *a, llmb_stream_t stream_) {
         if (!a->rope_cs || !a->k_cache || !a->v_cache || a->head_dim <= 0 || (a->head_dim & 1) ||
             a->n != a->n_q + 2 * a->n_kv || a->n_q % 32 || a->n_kv % 32)
             return LLMB_ERR_INVALID;
-    } else if (a->epilogue != LLMB_EPI_STORE && a->epilogue != LLMB_EPI_RESIDUAL && !dual) {
+    } else if (a->epilogue != LLMB_EPI_STORE && a->epilogue != LLMB_EPI_RESIDUAL && a->epilogue != LLMB_EPI_TP_SCATTER && !dual) {
         return LLMB_ERR_INVALID;
     }
+    // A handful of rows (batched decode): the weight-streaming kernel with the operands swapped
+    if (small_m) return launch_gemm_smallm(a, static_cast<cudaStream_t>(stream_));
     // Small grids: with a workspace, 128-wide tiles and K split across CTAs until the SMs are covered
     // (every CTA then streams its own weights and only its slice of the activations); without one, the
     // widest tile that still gives every SM a CTA.

@@ -23,6 +23,8 @@ rmsnorm_rows_kernel(const __half *__restrict__ x, const __half *__restrict__ gam
     extern __shared__ float norm_part[];  // n_pow2 partials (d / 4 real ones, zero padded)
     __shared__ float rms_s;
     const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();  // x is the previous kernel's output
     const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * d);
     const int nchunks = d >> 3;
     for (int c = tid; c < (n_pow2 >> 1); c += kNormThreads) {
@@ -263,10 +265,10 @@ extern "C" int llmb_rmsnorm_rows(const uint16_t *d_x, const uint16_t *d_gamma, u
         set_last_error("llmb_rmsnorm_rows: d above 40960 is not supported");
         return LLMB_ERR_UNSUPPORTED;
     }
-    rmsnorm_rows_kernel<<<m, kNormThreads, (size_t)n_pow2 * 4, static_cast<cudaStream_t>(stream_)>>>(
-        reinterpret_cast<const __half *>(d_x), reinterpret_cast<const __half *>(d_gamma), reinterpret_cast<__half *>(d_y), d,
-        n_pow2, eps);
-    LLMB_CUDA_OK(cudaGetLastError());
+    // launched with programmatic stream serialization: the kernel waits for its predecessor itself
+    LLMB_CUDA_OK(launch_pdl(rmsnorm_rows_kernel, dim3(m), dim3(kNormThreads), (size_t)n_pow2 * 4, static_cast<cudaStream_t>(stream_),
+                            true, reinterpret_cast<const __half *>(d_x), reinterpret_cast<const __half *>(d_gamma),
+                            reinterpret_cast<__half *>(d_y), d, n_pow2, eps));
     return LLMB_OK;
 }
 

@@ -142,6 +142,13 @@ class Cache:
             check(-r, "cache_sample_next_token")
         return r
 
+    def sample_device(self, temperature=0.7, top_k=50, top_p=0.9, seed=0, draw=0):
+        """The same sampling chain as sample(), run by one kernel on the device logits of the last step."""
+        r = lib.cache_sample_next_token_device(self.ptr, temperature, top_k, top_p, seed, draw)
+        if r < 0:
+            check(-r, "cache_sample_next_token_device")
+        return r
+
     def enable_hidden_dump(self, on=True):
         check(lib.cache_enable_hidden_dump(self.ptr, 1 if on else 0), "cache_enable_hidden_dump")
 
@@ -171,6 +178,10 @@ class Cache:
     def batch_init(self, n_seqs):
         check(lib.cache_batch_init(self.ptr, int(n_seqs)), "cache_batch_init")
         self.n_seqs = int(n_seqs)
+
+    def batch_set_split_len(self, split_len):
+        """Cache rows per attention CTA of the batched step (a power of two, 32..512)."""
+        check(lib.cache_batch_set_split_len(self.ptr, int(split_len)), "cache_batch_set_split_len")
 
     def batch_prefill(self, prompts):
         """prompts: [n_seqs][n_tokens] ids; the last token of each stays pending as the next step's input."""

@@ -51,6 +51,7 @@ struct Engine {
     float *rope_cs = nullptr;
     int *d_pos = nullptr, *d_next = nullptr, *d_history = nullptr;
     void *attn_scratch = nullptr;
+    void *sample_scratch = nullptr;  // device sampler: result code + [vocab] probabilities
     int max_splits = 0;
     // whole-step persistent kernel
     LlmbLayer *d_layers = nullptr;
@@ -92,6 +93,7 @@ struct Engine {
     int *bt_pos = nullptr, *bt_tok = nullptr, *bt_history = nullptr;  // [n_seqs], [n_seqs], [n_seqs][max_seq + 1]
     void *bt_attn_scratch = nullptr;
     int bt_max_splits = 0;
+    int bt_split_len = 256;                             // cache rows per attention CTA (a power of two, 32..512)
     std::vector<int> bt_len;                            // rows in the cache per sequence (host view)
     std::map<int, cudaGraphExec_t> bt_graphs;           // key: attention bucket
 };
@@ -306,12 +308,19 @@ int set_device_int(Engine *e, int *dst, int value) {
     return LLMB_OK;
 }
 
-// The block path needs tile-aligned projection shapes and all of the model on this GPU.
-bool prefill_supported(const Engine *e) {
+// The row paths need tile-aligned projection shapes (this rank's shares under tensor parallelism).
+bool rows_shapes_ok(const Engine *e) {
     const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
-    return e->tp_size == 1 && !e->hidden_dump && (e->hd == 64 || e->hd == 128) && (n_q + 2 * n_kv) % 128 == 0 &&
-           e->d % 128 == 0 && e->ffn % 128 == 0 && n_q % 64 == 0 && n_kv % 32 == 0;
+    return !e->hidden_dump && (e->hd == 64 || e->hd == 128) && (n_q + 2 * n_kv) % 128 == 0 && e->d % 128 == 0 &&
+           e->ffn % 128 == 0 && n_q % 64 == 0 && n_kv % 32 == 0 && e->vocab % 8 == 0;
 }
+
+// Blocks of up to 1024 rows: all of the model on this GPU.
+bool prefill_supported(const Engine *e) { return e->tp_size == 1 && rows_shapes_ok(e); }
+
+// Tensor parallel: blocks of up to 32 rows through the weight-streaming projections with the all-reduce
+// fused as peer stores (gemm_smallm.cu LLMB_EPI_TP_SCATTER + tp_rows.cu).
+bool tp_rows_supported(const Engine *e) { return e->tp_size > 1 && e->tp_connected && rows_shapes_ok(e); }
 
 void free_prefill_buffers(Engine *e) {
     cudaFree(e->pf_x); cudaFree(e->pf_xn); cudaFree(e->pf_q); cudaFree(e->pf_attn); cudaFree(e->pf_h);
@@ -418,6 +427,95 @@ int prefill_rows(Engine *e, int from, int to, const int *ids, __half *kbase, __h
     return LLMB_OK;
 }
 
+// One projection of the small-row paths; fills the fields every call shares.
+LlmbGemmArgs small_gemm(Engine *e, const void *a, const void *b, void *c, int m, int n, int k, int epilogue) {
+    LlmbGemmArgs g = {};
+    g.a = reinterpret_cast<const uint16_t *>(a);
+    g.b = reinterpret_cast<const uint16_t *>(b);
+    g.c = reinterpret_cast<uint16_t *>(c);
+    g.m = m; g.n = n; g.k = k;
+    g.epilogue = epilogue;
+    g.workspace = e->pf_ws; g.workspace_bytes = e->pf_ws_bytes;
+    g.use_pdl = 1;
+    if (epilogue == LLMB_EPI_TP_SCATTER) {
+        g.tp_rank = e->tp_rank; g.tp_size = e->tp_size;
+        for (int r = 0; r < e->tp_size; ++r) g.tp_peers[r] = e->peers[r];
+    }
+    return g;
+}
+
+// o_proj / down_proj of `m` rows and what follows it: single GPU = residual epilogue, then the RMSNorm of the
+// new rows if `gamma`; tensor parallel = partial sums scattered to every rank, then the gather kernel (sum in
+// rank order + residual + RMSNorm).  `xi` counts the exchanges of the step.
+int row_parallel_projection(Engine *e, const void *a, const void *w, int m, int k, const void *gamma, int &xi) {
+    const Llama3Config &c = e->model->config;
+    auto u16 = [](const void *p) { return reinterpret_cast<const uint16_t *>(p); };
+    int rc;
+    if (e->tp_size > 1) {
+        LlmbGemmArgs g = small_gemm(e, a, w, nullptr, m, e->d, k, LLMB_EPI_TP_SCATTER);
+        g.tp_index = xi;
+        if ((rc = llmb_gemm_f16(&g, e->stream))) return rc;
+        rc = llmb_tp_gather_rows(e->exchange, e->tp_size, xi, reinterpret_cast<uint16_t *>(e->pf_x), u16(gamma),
+                                 reinterpret_cast<uint16_t *>(e->pf_xn), m, e->d, c.eps, e->tag_poll_limit, 1, e->stream);
+        ++xi;
+        return rc;
+    }
+    LlmbGemmArgs g = small_gemm(e, a, w, e->pf_x, m, e->d, k, LLMB_EPI_RESIDUAL);
+    if ((rc = llmb_gemm_f16(&g, e->stream))) return rc;
+    if (gamma) rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(gamma), reinterpret_cast<uint16_t *>(e->pf_xn), m, e->d, c.eps, e->stream);
+    return rc;
+}
+
+// Tensor parallel prompt phase: history positions [from, to) in blocks of up to 32 rows.  Every block streams
+// this rank's weight shards once (the same kernels as the batched decode step) and attends causally over the
+// rank's KV heads; no logits.
+int prefill_rows_tp(Engine *e, int from, int to, const int *ids, __half *kbase, __half *vbase, size_t layer_stride) {
+    Llama3 *m = e->model;
+    const Llama3Config &c = m->config;
+    cudaStream_t s = e->stream;
+    const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    int rc = ensure_prefill_buffers(e, 32);
+    if (rc) return rc;
+    auto u16 = [](const void *p) { return reinterpret_cast<const uint16_t *>(p); };
+    auto u16w = [](void *p) { return reinterpret_cast<uint16_t *>(p); };
+    for (int p0 = from; p0 < to; p0 += 32) {
+        const int rows = std::min(32, to - p0);
+        if ((rc = llmb_iota_i32(e->pf_pos, p0, rows, s))) return rc;
+        if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), ids + p0, e->pf_pos, rows, e->d, e->embed_rows, e->hd,
+                                  c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 0, s)))
+            return rc;
+        if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(m->layers[0]->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), rows, e->d,
+                                    c.eps, s)))
+            return rc;
+        int xi = 0;
+        for (int l = 0; l < e->layers; ++l) {
+            const Llama3Layer *L = m->layers[l];
+            __half *kl = kbase + (size_t)l * layer_stride;
+            __half *vl = vbase + (size_t)l * layer_stride;
+            LlmbGemmArgs g = small_gemm(e, e->pf_xn, L->self_attn_q_proj->d_fp16_tensor, e->pf_q, rows, n_q + 2 * n_kv, e->d,
+                                        LLMB_EPI_ROPE_KV);
+            g.n_q = n_q; g.n_kv = n_kv; g.head_dim = e->hd;
+            g.rope_cs = e->pf_rope;
+            g.k_cache = u16w(kl); g.v_cache = u16w(vl);
+            g.pos0 = p0; g.max_pos = e->max_seq;
+            if ((rc = llmb_gemm_f16(&g, s))) return rc;
+            if ((rc = llmb_attn_prefill(u16(e->pf_q), u16(kl), u16(vl), rows, p0, e->nq, e->nkv, e->hd, u16w(e->pf_attn), s)))
+                return rc;
+            if ((rc = row_parallel_projection(e, e->pf_attn, L->self_attn_o_proj->d_fp16_tensor, rows, n_q,
+                                              L->post_attention_layernorm->d_fp16_tensor, xi)))
+                return rc;
+            LlmbGemmArgs f = small_gemm(e, e->pf_xn, L->mlp_gate_proj->d_fp16_tensor, e->pf_h, rows, e->ffn, e->d, LLMB_EPI_SWIGLU);
+            f.b2 = u16(L->mlp_up_proj->d_fp16_tensor);
+            if ((rc = llmb_gemm_f16(&f, s))) return rc;
+            const void *next_gamma = l + 1 < e->layers ? m->layers[l + 1]->input_layernorm->d_fp16_tensor : nullptr;
+            if ((rc = row_parallel_projection(e, e->pf_h, L->mlp_down_proj->d_fp16_tensor, rows, e->ffn, next_gamma, xi))) return rc;
+        }
+        if ((rc = llmb_tp_advance(e->exchange, e->tp_size, e->d, xi, 1, s))) return rc;
+        e->launches += 4 + 7 * e->layers;
+    }
+    return LLMB_OK;
+}
+
 // Feeds ids[from..to) (history rows from..to-1), logits only for the last one.
 int feed_tokens(Engine *e, const int *ids, int from, int to) {
     if (to <= from) return LLMB_ERR_INVALID;
@@ -432,6 +530,9 @@ int feed_tokens(Engine *e, const int *ids, int from, int to) {
     // all but the last token as blocks of rows; the last one through the decode step, for its logits
     if (e->batched_prefill && to - 1 - from >= e->prefill_min_rows && prefill_supported(e)) {
         if ((rc = prefill_rows(e, from, to - 1, e->d_history, e->kcache, e->vcache, (size_t)e->max_seq * e->nkv * e->hd))) return rc;
+        first = to - 1;
+    } else if (e->batched_prefill && to - 1 - from >= e->prefill_min_rows && tp_rows_supported(e)) {
+        if ((rc = prefill_rows_tp(e, from, to - 1, e->d_history, e->kcache, e->vcache, (size_t)e->max_seq * e->nkv * e->hd))) return rc;
         first = to - 1;
     }
     if ((rc = set_device_int(e, e->d_pos, first))) return rc;
@@ -469,6 +570,7 @@ void destroy_engine(Engine *e) {
     cudaFree(e->x); cudaFree(e->q); cudaFree(e->attn); cudaFree(e->h);
     cudaFree(e->rope_cs); cudaFree(e->d_pos); cudaFree(e->d_next); cudaFree(e->d_history);
     cudaFree(e->attn_scratch); cudaFree(e->hidden); cudaFree(e->d_layers); cudaFree(e->step_scratch);
+    cudaFree(e->sample_scratch);
     for (int r = 0; r < e->tp_size; ++r)
         if (e->tp_connected && r != e->tp_rank && e->peers[r]) cudaIpcCloseMemHandle(e->peers[r]);
     cudaFree(e->exchange); cudaFree(e->x_alt); cudaFree(e->trace);
@@ -795,6 +897,41 @@ extern "C" int cache_sample_next_token(CudaCache *cache, float temperature, int 
     return rc ? -rc : token;
 }
 
+// The same chain on the device (llmb_sample_logits): the logits never leave the GPU, only the 4-byte token
+// comes back, and it is also written over the greedy token in the device history, so that
+// inference_continue() goes on from the sampled token.  Falls back to nothing: a step the device kernel
+// cannot take (status UNSUPPORTED) is reported to the caller, who can use cache_sample_next_token().
+extern "C" int cache_sample_next_token_device(CudaCache *cache, float temperature, int top_k, float top_p, uint64_t seed,
+                                              uint64_t draw) {
+    Engine *e = eng(cache);
+    if (!e) return -LLMB_ERR_INVALID;
+    if (e->consumed.empty()) {
+        set_last_error("cache_sample_next_token_device: no decode step has produced logits yet");
+        return -LLMB_ERR_INVALID;
+    }
+    if (e->tp_size > 1) {
+        set_last_error("cache_sample_next_token_device: a tensor-parallel rank holds a slice of the logits only");
+        return -LLMB_ERR_UNSUPPORTED;
+    }
+    if (!e->sample_scratch) {
+        cudaError_t ce = cudaMalloc(&e->sample_scratch, llmb_sample_scratch_bytes(e->vocab));
+        if (ce != cudaSuccess) return -cuda_fail(ce, __FILE__, __LINE__);
+    }
+    int rc = llmb_sample_logits(reinterpret_cast<const uint16_t *>(e->logits), e->vocab, temperature, top_k, top_p, seed, draw,
+                                e->sample_scratch, e->d_next, e->d_pos, e->d_history, e->max_seq + 1, 0, e->stream);
+    if (rc) return -rc;
+    cudaError_t ce = cudaMemcpyAsync(e->h_next, e->d_next, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(e->h_next + 2, e->sample_scratch, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+    if (ce != cudaSuccess) return -cuda_fail(ce, __FILE__, __LINE__);
+    if (e->h_next[2] != 0) {
+        set_last_error(e->h_next[2] == 1 ? "device sampler: exp(logit / temperature) overflowed FP32; raise the temperature"
+                                         : "device sampler: the top-p prefix runs past 1024 entries; use cache_sample_next_token");
+        return -LLMB_ERR_UNSUPPORTED;
+    }
+    return e->h_next[0];
+}
+
 extern "C" long long cache_kernel_launches(const CudaCache *cache) {
     const Engine *e = eng(cache);
     return e ? e->launches : -1;
@@ -930,11 +1067,9 @@ extern "C" int inference_continue(Llama3 *m, CudaCache *cache, int n_steps, int 
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-SplitPlan plan_batch_splits(int len) {
+SplitPlan plan_batch_splits(int len, int split_len) {
     int bucket = 512;
     while (bucket < len) bucket <<= 1;
-    int split_len = bucket / 8;  // many (sequence, head) pairs fill the GPU already: few, long splits
-    if (split_len < 128) split_len = 128;
     return {bucket, bucket / split_len, split_len};
 }
 
@@ -944,80 +1079,55 @@ int enqueue_batch_step(Engine *e, const SplitPlan &sp) {
     cudaStream_t s = e->stream;
     const int B = e->bt_seqs;
     const int n_q = e->nq * e->hd, n_kv = e->nkv * e->hd;
+    const bool tp = e->tp_size > 1;
     auto u16 = [](const void *p) { return reinterpret_cast<const uint16_t *>(p); };
     auto u16w = [](void *p) { return reinterpret_cast<uint16_t *>(p); };
     int rc;
     if ((rc = llmb_embed_rope(u16(m->embed_tokens->d_fp16_tensor), e->bt_tok, e->bt_pos, B, e->d, e->embed_rows, e->hd,
-                              c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 0, s)))
+                              c.rope_theta, u16w(e->pf_x), e->pf_rope, 0, 1, s)))
+        return rc;
+    if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(m->layers[0]->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), B, e->d, c.eps, s)))
         return rc;
     const size_t layer_stride = (size_t)B * e->max_seq * n_kv;
+    int xi = 0;  // tensor parallel: exchanges of this step so far
     for (int l = 0; l < e->layers; ++l) {
         const Llama3Layer *L = m->layers[l];
         __half *kl = e->bt_kcache + (size_t)l * layer_stride;
         __half *vl = e->bt_vcache + (size_t)l * layer_stride;
-        if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->input_layernorm->d_fp16_tensor), u16w(e->pf_xn), B, e->d, c.eps, s)))
-            return rc;
-        LlmbGemmArgs g = {};
-        g.a = u16(e->pf_xn);
-        g.b = u16(L->self_attn_q_proj->d_fp16_tensor);
-        g.c = u16w(e->pf_q);
-        g.m = B; g.n = n_q + 2 * n_kv; g.k = e->d;
-        g.epilogue = LLMB_EPI_ROPE_KV;
+        LlmbGemmArgs g = small_gemm(e, e->pf_xn, L->self_attn_q_proj->d_fp16_tensor, e->pf_q, B, n_q + 2 * n_kv, e->d, LLMB_EPI_ROPE_KV);
         g.n_q = n_q; g.n_kv = n_kv; g.head_dim = e->hd;
         g.rope_cs = e->pf_rope;
         g.k_cache = u16w(kl); g.v_cache = u16w(vl);
         g.row_pos = e->bt_pos; g.seq_stride = e->max_seq; g.max_pos = e->max_seq;
-        g.workspace = e->pf_ws; g.workspace_bytes = e->pf_ws_bytes;
         if ((rc = llmb_gemm_f16(&g, s))) return rc;
         if ((rc = llmb_attn_decode_batch(u16(e->pf_q), u16(kl), u16(vl), e->bt_pos, B, (size_t)e->max_seq, e->nq, e->nkv, e->hd,
-                                         sp.n_splits, sp.split_len, u16w(e->pf_attn), e->bt_attn_scratch, 0, s)))
+                                         sp.n_splits, sp.split_len, u16w(e->pf_attn), e->bt_attn_scratch, 1, s)))
             return rc;
-        LlmbGemmArgs o = {};
-        o.a = u16(e->pf_attn);
-        o.b = u16(L->self_attn_o_proj->d_fp16_tensor);
-        o.c = u16w(e->pf_x);
-        o.m = B; o.n = e->d; o.k = n_q;
-        o.epilogue = LLMB_EPI_RESIDUAL;
-        o.workspace = e->pf_ws; o.workspace_bytes = e->pf_ws_bytes;
-        if ((rc = llmb_gemm_f16(&o, s))) return rc;
-        if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(L->post_attention_layernorm->d_fp16_tensor), u16w(e->pf_xn), B, e->d,
-                                    c.eps, s)))
+        if ((rc = row_parallel_projection(e, e->pf_attn, L->self_attn_o_proj->d_fp16_tensor, B, n_q,
+                                          L->post_attention_layernorm->d_fp16_tensor, xi)))
             return rc;
-        LlmbGemmArgs f = {};
-        f.a = u16(e->pf_xn);
-        f.b = u16(L->mlp_gate_proj->d_fp16_tensor);
+        LlmbGemmArgs f = small_gemm(e, e->pf_xn, L->mlp_gate_proj->d_fp16_tensor, e->pf_h, B, e->ffn, e->d, LLMB_EPI_SWIGLU);
         f.b2 = u16(L->mlp_up_proj->d_fp16_tensor);
-        f.c = u16w(e->pf_h);
-        f.m = B; f.n = e->ffn; f.k = e->d;
-        f.epilogue = LLMB_EPI_SWIGLU;
-        f.workspace = e->pf_ws; f.workspace_bytes = e->pf_ws_bytes;
         if ((rc = llmb_gemm_f16(&f, s))) return rc;
-        LlmbGemmArgs dn = {};
-        dn.a = u16(e->pf_h);
-        dn.b = u16(L->mlp_down_proj->d_fp16_tensor);
-        dn.c = u16w(e->pf_x);
-        dn.m = B; dn.n = e->d; dn.k = e->ffn;
-        dn.epilogue = LLMB_EPI_RESIDUAL;
-        dn.workspace = e->pf_ws; dn.workspace_bytes = e->pf_ws_bytes;
-        if ((rc = llmb_gemm_f16(&dn, s))) return rc;
+        const void *next_gamma = l + 1 < e->layers ? m->layers[l + 1]->input_layernorm->d_fp16_tensor : m->norm->d_fp16_tensor;
+        if ((rc = row_parallel_projection(e, e->pf_h, L->mlp_down_proj->d_fp16_tensor, B, e->ffn, next_gamma, xi))) return rc;
     }
-    if ((rc = llmb_rmsnorm_rows(u16(e->pf_x), u16(m->norm->d_fp16_tensor), u16w(e->pf_xn), B, e->d, c.eps, s))) return rc;
-    LlmbGemmArgs lm = {};
-    lm.a = u16(e->pf_xn);
-    lm.b = u16(m->lm_head->d_fp16_tensor);
-    lm.c = u16w(e->bt_logits);
-    lm.m = B; lm.n = e->vocab; lm.k = e->d;
-    lm.epilogue = LLMB_EPI_STORE;
-    lm.workspace = e->pf_ws; lm.workspace_bytes = e->pf_ws_bytes;
+    LlmbGemmArgs lm = small_gemm(e, e->pf_xn, m->lm_head->d_fp16_tensor, e->bt_logits, B, e->vocab, e->d, LLMB_EPI_STORE);
     if ((rc = llmb_gemm_f16(&lm, s))) return rc;
     // greedy token of every sequence -> next step's input; positions advance; history keeps what was sampled
-    return llmb_argmax_rows_f16(u16(e->bt_logits), e->vocab, B, e->bt_tok, e->bt_pos, e->bt_history, e->max_seq + 1, 0, s);
+    if (tp) {
+        if ((rc = llmb_tp_argmax_rows(e->peers, e->tp_rank, e->tp_size, e->d, xi, u16(e->bt_logits), e->vocab, e->tp_rank * e->vocab, B,
+                                      e->bt_tok, e->bt_pos, e->bt_history, e->max_seq + 1, e->tag_poll_limit, 1, s)))
+            return rc;
+        return llmb_tp_advance(e->exchange, e->tp_size, e->d, xi + 1, 1, s);
+    }
+    return llmb_argmax_rows_f16(u16(e->bt_logits), e->vocab, B, e->bt_tok, e->bt_pos, e->bt_history, e->max_seq + 1, 1, s);
 }
 
 // One batched step for sequences whose longest has `len` rows after it.
 int run_batch_step(Engine *e, int len) {
-    const SplitPlan sp = plan_batch_splits(len);
-    e->launches += 2 + 7 * e->layers + 3;
+    const SplitPlan sp = plan_batch_splits(len, e->bt_split_len);
+    e->launches += 2 + 7 * e->layers + 2 + (e->tp_size > 1 ? 1 : 0);
     if (!e->use_graph) return enqueue_batch_step(e, sp);
     auto it = e->bt_graphs.find(sp.bucket);
     if (it == e->bt_graphs.end()) {
@@ -1040,9 +1150,7 @@ int run_batch_step(Engine *e, int len) {
     return LLMB_OK;
 }
 
-bool batch_supported(const Engine *e) {
-    return prefill_supported(e) && e->vocab % 128 == 0;
-}
+bool batch_supported(const Engine *e) { return prefill_supported(e) || tp_rows_supported(e); }
 
 }  // namespace
 
@@ -1050,8 +1158,8 @@ extern "C" int cache_batch_init(CudaCache *cache, int n_seqs) {
     Engine *e = eng(cache);
     if (!e || n_seqs < 1 || n_seqs > 128) return LLMB_ERR_INVALID;
     if (!batch_supported(e)) {
-        set_last_error("cache_batch_init: batched decode needs the whole model on this GPU (tp_size 1), head_dim 64 or 128 and "
-                       "projection widths (q+k+v, d_model, ffn, vocab) that are multiples of 128");
+        set_last_error("cache_batch_init: batched decode needs head_dim 64 or 128, projection widths (this rank's q+k+v, d_model, "
+                       "ffn) that are multiples of 128 and, under tensor parallelism, cache_tp_connect() first");
         return LLMB_ERR_UNSUPPORTED;
     }
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
@@ -1065,7 +1173,7 @@ extern "C" int cache_batch_init(CudaCache *cache, int n_seqs) {
     e->bt_seqs = 0;
     const size_t n_kv = (size_t)e->nkv * e->hd;
     const size_t kv_bytes = (size_t)e->layers * n_seqs * e->max_seq * n_kv * 2;
-    e->bt_max_splits = plan_batch_splits(e->max_seq).n_splits;
+    e->bt_max_splits = plan_batch_splits(e->max_seq, 32).n_splits;  // sized for the shortest split the engine may be set to
     const size_t scratch = llmb_attn_decode_batch_scratch_bytes(n_seqs, e->nq, e->nkv, e->hd, e->bt_max_splits);
     cudaError_t ce = cudaSuccess;
     auto alloc = [&](void **p, size_t bytes) {
@@ -1088,6 +1196,16 @@ extern "C" int cache_batch_init(CudaCache *cache, int n_seqs) {
     return LLMB_OK;
 }
 
+extern "C" int cache_batch_set_split_len(CudaCache *cache, int split_len) {
+    Engine *e = eng(cache);
+    if (!e || split_len < 32 || split_len > 512 || (split_len & (split_len - 1))) return LLMB_ERR_INVALID;
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    for (auto &kv : e->bt_graphs) cudaGraphExecDestroy(kv.second);  // the split geometry is baked into the captured steps
+    e->bt_graphs.clear();
+    e->bt_split_len = split_len;
+    return LLMB_OK;
+}
+
 // tokens: [n_seqs][n_tokens] host ids.  All but the last token of every sequence go through the block
 // path into that sequence's cache; the last one is left as the input of the next cache_batch_step().
 extern "C" int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_tokens) {
@@ -1105,10 +1223,12 @@ extern "C" int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_to
         int *hist = e->bt_history + (size_t)b * (e->max_seq + 1);
         LLMB_CUDA_OK(cudaMemcpyAsync(hist, tokens + (size_t)b * n_tokens, sizeof(int) * (size_t)n_tokens, cudaMemcpyHostToDevice,
                                      e->stream));
-        if (n_tokens > 1 &&
-            (rc = prefill_rows(e, 0, n_tokens - 1, hist, e->bt_kcache + (size_t)b * e->max_seq * n_kv,
-                               e->bt_vcache + (size_t)b * e->max_seq * n_kv, (size_t)B * e->max_seq * n_kv)))
-            return rc;
+        if (n_tokens > 1) {
+            __half *kb = e->bt_kcache + (size_t)b * e->max_seq * n_kv, *vb = e->bt_vcache + (size_t)b * e->max_seq * n_kv;
+            rc = e->tp_size > 1 ? prefill_rows_tp(e, 0, n_tokens - 1, hist, kb, vb, (size_t)B * e->max_seq * n_kv)
+                                : prefill_rows(e, 0, n_tokens - 1, hist, kb, vb, (size_t)B * e->max_seq * n_kv);
+            if (rc) return rc;
+        }
         last[(size_t)b] = tokens[(size_t)b * n_tokens + n_tokens - 1];
     }
     LLMB_CUDA_OK(cudaMemcpyAsync(e->bt_tok, last.data(), sizeof(int) * (size_t)B, cudaMemcpyHostToDevice, e->stream));

@@ -299,3 +299,82 @@ def test_8b_layer_shapes_block_prefill(pkg, oracle, weights_8b_l2):
     want_tok = int(oracle.lib().oracle_argmax_fp16(ref_logits[0].ctypes.data, len(ref_logits[0])))
     assert a[0] == want_tok
     model.close()
+
+
+@pytest.mark.parametrize("m,use_ws,use_pdl", [(1, False, 0), (7, True, 1), (32, True, 1), (20, False, 1)])
+def test_gemm_small_m_weight_stream_all_epilogues(pkg, oracle, m, use_ws, use_pdl):
+    """m <= 32 rows take the weight-streaming kernel (weights as the 128-row MMA operand, K split across CTAs
+    when a workspace is given).  Every epilogue, twice in a row on the same workspace, with and without
+    programmatic dependent launch; the batched-decode form of the cache append (one sequence per row)."""
+    ws = torch.zeros(4096 + 148 * 131072, dtype=torch.uint8, device="cuda") if use_ws else None
+    kw = dict(use_pdl=use_pdl, **(dict(workspace=ws, workspace_bytes=ws.numel()) if use_ws else {}))
+    for rep in range(2):
+        # store: k long enough for several K slices
+        n, k = 384, 4096
+        a, b = mats(oracle, m, n, k, 40 + rep)
+        out = torch.full((m + 2, n), 0x7BFF, dtype=torch.int16, device="cuda")
+        gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_STORE, **kw)
+        want = matmul64(a, b)
+        got = host_u16(out)
+        assert_close_fp16(got[:m], want, what="small-m store", abs_tol=tc_tol(want, k))
+        assert (got[m:] == 0x7BFF).all()
+        # residual
+        n, k = 256, 1024
+        a, b = mats(oracle, m, n, k, 50 + rep)
+        res = oracle.synth_fp16(7, 3, m * n, std=1.0).reshape(m, n)
+        out = dev(res.copy())
+        gemm(pkg, a=dev(a), b=dev(b), c=out, m=m, n=n, k=k, epilogue=EPI_RESIDUAL, **kw)
+        acc = matmul64(a, b)
+        want = acc.astype(np.float16).astype(np.float64) + f16(res).astype(np.float64)
+        assert_close_fp16(host_u16(out).reshape(m, n), want, what="small-m residual", max_frac=0.1,
+                          abs_tol=np.abs(acc) * 2.0 ** -10 + tc_tol(acc, k))
+        # SwiGLU
+        n, k = 512, 2048
+        a, b = mats(oracle, m, n, k, 60 + rep)
+        b2 = oracle.synth_fp16(8, 4, n * k, std=0.02).reshape(n, k)
+        out = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+        gemm(pkg, a=dev(a), b=dev(b), b2=dev(b2), c=out, m=m, n=n, k=k, epilogue=EPI_SWIGLU, **kw)
+        g, u = matmul64(a, b), matmul64(a, b2)
+        want = g / (1.0 + np.exp(-g)) * u
+        assert_close_fp16(host_u16(out).reshape(m, n), want, what="small-m swiglu", abs_tol=tc_tol(want, k))
+        # RoPE + cache append, one sequence per row: row r goes to cache row r * seq_stride + row_pos[r]
+        hd, nqh, nkvh, seq_stride, k = 64, 4, 2, 16, 512
+        n_q, n_kv = nqh * hd, nkvh * hd
+        n = n_q + 2 * n_kv
+        a, b = mats(oracle, m, n, k, 70 + rep)
+        row_pos = ((np.arange(m) * 5 + rep) % seq_stride).astype(np.int32)
+        i = np.arange(hd // 2, dtype=np.float32)
+        freq = (1.0 / np.power(np.float32(500000.0), 2.0 * i / np.float32(hd))).astype(np.float32)
+        ang = (row_pos.astype(np.float32)[:, None] * freq[None, :]).astype(np.float32)
+        cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+        q_out = torch.zeros((m, n_q), dtype=torch.int16, device="cuda")
+        kc = torch.zeros((m * seq_stride, n_kv), dtype=torch.int16, device="cuda")
+        vc = torch.zeros((m * seq_stride, n_kv), dtype=torch.int16, device="cuda")
+        gemm(pkg, a=dev(a), b=dev(b), c=q_out, m=m, n=n, k=k, epilogue=EPI_ROPE_KV, n_q=n_q, n_kv=n_kv, head_dim=hd,
+             rope_cs=dev(cs), k_cache=kc, v_cache=vc, row_pos=dev(row_pos), seq_stride=seq_stride, max_pos=seq_stride, **kw)
+        y = matmul64(a, b).astype(np.float16).astype(np.float64)
+
+        def rope(block, heads):
+            r = block.reshape(m, heads, hd // 2, 2)
+            c, s = cs[:, None, :, 0].astype(np.float64), cs[:, None, :, 1].astype(np.float64)
+            o = np.empty_like(r)
+            o[..., 0] = c * r[..., 0] - s * r[..., 1]
+            o[..., 1] = s * r[..., 0] + c * r[..., 1]
+            return o.reshape(m, heads * hd)
+
+        def pair_tol(block):
+            mag = np.abs(block).reshape(m, -1, 2).sum(axis=2, keepdims=True) * 2.0 ** -10
+            return np.broadcast_to(mag, (m, block.shape[1] // 2, 2)).reshape(m, -1) + tc_tol(y, k)
+
+        assert_close_fp16(host_u16(q_out).reshape(m, n_q), rope(y[:, :n_q], nqh), what="small-m q rope", max_frac=0.1,
+                          abs_tol=pair_tol(y[:, :n_q]))
+        rows = np.arange(m) * seq_stride + row_pos
+        kgot, vgot = host_u16(kc).reshape(m * seq_stride, n_kv), host_u16(vc).reshape(m * seq_stride, n_kv)
+        assert_close_fp16(kgot[rows], rope(y[:, n_q:n_q + n_kv], nkvh), what="small-m k rope", max_frac=0.1,
+                          abs_tol=pair_tol(y[:, n_q:n_q + n_kv]))
+        assert_close_fp16(vgot[rows], y[:, n_q + n_kv:], what="small-m v", abs_tol=tc_tol(y, k))
+        untouched = np.ones(m * seq_stride, dtype=bool)
+        untouched[rows] = False
+        assert not kgot[untouched].any() and not vgot[untouched].any()
+        if use_ws:
+            assert not host_u16(ws[:4096].view(torch.int16)).any(), "arrival counters not back to zero"

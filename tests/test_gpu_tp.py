@@ -90,12 +90,16 @@ def _rank_main(rank, world, port, cfg_name, n_prompt, n_steps, result_path, shar
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("cfg_name,world", [("tiny", 2), ("llama3_8b_l2", 2), ("llama3_8b_l2", 4), ("llama3_8b_l2", 8)])
-def test_tensor_parallel_decode_matches_oracle(cfg_name, world, tmp_path):
+# n_prompt 16: every prompt token through the whole-step kernel; 45: the prompt as blocks of 32 rows through the
+# weight-streaming projections with the all-reduce fused as peer stores, then the whole-step kernel
+@pytest.mark.parametrize("cfg_name,world,n_prompt", [("tiny", 2, 16), ("llama3_8b_l2", 2, 16), ("llama3_8b_l2", 4, 16),
+                                                     ("llama3_8b_l2", 8, 16), ("llama3_70b_l2", 2, 16), ("llama3_70b_l2", 8, 16),
+                                                     ("tiny", 2, 45), ("llama3_8b_l2", 2, 45), ("llama3_8b_l2", 8, 45)])
+def test_tensor_parallel_decode_matches_oracle(cfg_name, world, n_prompt, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
     result = tmp_path / "r.txt"
-    mp.spawn(_rank_main, args=(world, _free_port(), cfg_name, 16, 6, str(result)), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), cfg_name, n_prompt, 6, str(result)), nprocs=world, join=True)
     status, worst, toks = result.read_text().split(" ", 2)
     print("TP=%d %s: worst |dlogit| %s, greedy %s" % (world, cfg_name, worst, toks))
     assert status == "1", "worst |dlogit| %s" % worst
@@ -111,4 +115,78 @@ def test_tensor_parallel_streaming_load_from_a_shard_file(tmp_path):
     result = tmp_path / "r.txt"
     mp.spawn(_rank_main, args=(2, _free_port(), "tiny", 16, 6, str(result), shard), nprocs=2, join=True)
     status, worst, toks = result.read_text().split(" ", 2)
+    assert status == "1", "worst |dlogit| %s" % worst
+
+
+def _rank_batch(rank, world, port, cfg_name, n_seqs, n_prompt, n_steps, result_path):
+    """Batched decode under tensor parallelism: every rank feeds the same tokens; rank 0 puts the ranks' vocabulary
+    slices together and compares every sequence with its own oracle run."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from conftest import load_package
+    from oracle import oracle_lib as oracle
+    pkg = load_package()
+    cfg = pkg.CONFIGS[cfg_name]
+    vocab_ids = cfg.embed_rows or cfg.vocab
+    seqs = np.stack([oracle.synth_tokens(100 + b, n_prompt + n_steps, vocab_ids) for b in range(n_seqs)])
+    model = pkg.Model.synthetic(cfg, seed=0, max_seq=128, tp_rank=rank, tp_size=world)
+    cache = pkg.Cache(model)
+    cache.tp_connect()
+    ref = None
+    if rank == 0:
+        weights = oracle.Weights(cfg, seed=0, keep_file=False)
+        ref = [oracle.forward(weights, seqs[b], first_logit_row=n_prompt - 1)[0] for b in range(n_seqs)]
+    dist.barrier()
+    cache.batch_init(n_seqs)
+    cache.batch_prefill(seqs[:, :n_prompt])
+    ok, worst = True, 0.0
+    for step in range(n_steps + 1):
+        feed = None if step == 0 else seqs[:, n_prompt + step - 1]
+        nxt, mine = cache.batch_step(feed)
+        parts = [torch.empty(mine.shape, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(mine.astype(np.int32)))
+        toks = [torch.empty(n_seqs, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(toks, torch.from_numpy(nxt.astype(np.int32)))
+        ok &= all(torch.equal(toks[0], t) for t in toks)   # every rank picked the same tokens
+        if rank == 0:
+            logits = torch.cat(parts, dim=1).numpy().astype(np.uint16)
+            for b in range(n_seqs):
+                want = ref[b][step]
+                diff = float(np.abs(oracle.f16(logits[b]) - oracle.f16(want)).max())
+                worst = max(worst, diff)
+                want_tok = int(oracle.lib().oracle_argmax_fp16(want.ctypes.data, len(want)))
+                ok &= int(nxt[b]) == int(oracle.lib().oracle_argmax_fp16(np.ascontiguousarray(logits[b]).ctypes.data, len(want)))
+                if int(nxt[b]) != want_tok:
+                    top2 = np.sort(oracle.f16(want))[-2:]
+                    ok &= bool(top2[1] - top2[0] <= 2 * diff + 1e-3)
+    # device-resident greedy run: the sampled tokens are fed back on every rank alike
+    cache.batch_prefill(seqs[:, :n_prompt])
+    dist.barrier()
+    greedy, _ = cache.batch_greedy(4)
+    every = [torch.empty(greedy.shape, dtype=torch.int32) for _ in range(world)]
+    dist.all_gather(every, torch.from_numpy(greedy.astype(np.int32)))
+    ok &= all(torch.equal(every[0], t) for t in every)
+    st = __import__("ctypes").c_int(0)
+    pkg.lib.llmb_device_status(__import__("ctypes").byref(st))
+    ok &= st.value == 0
+    flag = torch.tensor([1 if (ok and worst <= LOGIT_TOL) else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        with open(result_path, "w") as f:
+            f.write("%d %.5g" % (int(flag.item()), worst))
+    cache.close()
+    model.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg_name,world,n_seqs,n_prompt", [("tiny", 2, 5, 40), ("llama3_8b_l2", 2, 32, 9), ("llama3_8b_l2", 8, 8, 9),
+                                                            ("llama3_70b_l2", 8, 8, 9)])
+def test_tensor_parallel_batched_decode_matches_oracle(cfg_name, world, n_seqs, n_prompt, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    result = tmp_path / "r.txt"
+    mp.spawn(_rank_batch, args=(world, _free_port(), cfg_name, n_seqs, n_prompt, 3, str(result)), nprocs=world, join=True)
+    status, worst = result.read_text().split(" ")
+    print("TP=%d %s batch %d: worst |dlogit| %s" % (world, cfg_name, n_seqs, worst))
     assert status == "1", "worst |dlogit| %s" % worst
