@@ -152,6 +152,11 @@ int llmb_attn_decode_batch(const uint16_t *d_q, const uint16_t *d_k_cache, const
                            int head_dim, int n_splits, int split_len, uint16_t *d_out, void *d_scratch, int use_pdl,
                            llmb_stream_t stream);
 
+/* Profiling aid: the following launches of the decode attention record per-CTA nanosecond stamps (entry,    */
+/* previous kernel complete, first tile landed, tiles done, partial published, merge done) into d_trace,       */
+/* 8 uint64 per CTA, CTA index = (seq * n_kv_heads + kv_head) * n_splits + split.  NULL (default) = off.       */
+int llmb_attn_decode_trace(void *d_trace);
+
 /* The same attention for callers that may not allocate device memory (a host whose own pool  */
 /* owns the device, a loop that cannot afford an allocation's synchronisation, a plug-in that  */
 /* only ever sees its input and output buffers): no workspace argument, the partial results     */

@@ -24,7 +24,7 @@ EPI_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_SWIGLU, EPI_TP_SCATTER = 0, 1, 2, 3, 4
 KERNEL_SYMBOLS = [
     "llmb_last_error", "llmb_device_status", "llmb_build_info", "llmb_bf16_to_fp16", "llmb_synth_bf16",
     "llmb_synth_fp16", "llmb_synth_2d", "llmb_fill_u16", "llmb_embed_rope", "llmb_gemv_f16", "llmb_attn_decode_scratch_bytes",
-    "llmb_attn_decode", "llmb_attn_decode_batch_scratch_bytes", "llmb_attn_decode_batch", "llmb_attn_decode_static", "llmb_argmax_rows_f16", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
+    "llmb_attn_decode", "llmb_attn_decode_batch_scratch_bytes", "llmb_attn_decode_batch", "llmb_attn_decode_trace", "llmb_attn_decode_static", "llmb_argmax_rows_f16", "llmb_argmax_f16", "llmb_advance_pos", "llmb_gemm_f16",
     "llmb_rmsnorm_rows", "llmb_tp_gather_rows", "llmb_tp_argmax_rows", "llmb_tp_advance", "llmb_attn_prefill", "llmb_iota_i32", "llmb_sample_logits_host", "llmb_sampler_uniform", "llmb_sample_scratch_bytes", "llmb_sample_logits", "llmb_decode_step_scratch_bytes", "llmb_decode_step_exchange_bytes", "llmb_decode_step",
 ]
 HOST_SYMBOLS = [
@@ -143,6 +143,7 @@ def _declare(l):
     l.llmb_attn_decode_batch_scratch_bytes.argtypes = [i32, i32, i32, i32, i32]
     l.llmb_attn_decode_batch_scratch_bytes.restype = sz
     l.llmb_attn_decode_batch.argtypes = [vp, vp, vp, vp, i32, sz, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+    l.llmb_attn_decode_trace.argtypes = [vp]
     l.llmb_argmax_rows_f16.argtypes = [vp, i32, i32, vp, vp, vp, i32, i32, vp]
     l.llmb_attn_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]
     l.llmb_argmax_f16.argtypes = [vp, i32, vp, vp, vp, i32, i32, vp]

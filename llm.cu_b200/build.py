@@ -32,6 +32,7 @@ HEADERS = [
     "csrc/gemv_common.cuh",
     "csrc/gemm_common.cuh",
     "csrc/tp_common.cuh",
+    "csrc/mma_common.cuh",
     "host/host_internal.h",
     "../include/llm_b200.h",
     "../include/llama3.h",

@@ -3,23 +3,27 @@
 //
 // Bound: HBM/L2 bandwidth on the cached K and V rows: algorithmic bytes per launch =
 // (pos + 1) * 2 * n_kv_heads * head_dim * 2.  At the context lengths of the benchmark configs
-// this is 1-4 % of a layer's weight bytes, so the kernel is shaped for latency: many small
-// CTAs, one pass, no N x N score buffer.
+// this is 1-4 % of a layer's weight bytes at batch 1 and a quarter of a step's bytes at 32 sequences:
+// one pass, no N x N score buffer, and the arithmetic on the tensor cores so that a CTA is bound by its
+// loads, not by instruction issue.
 //
-//   grid   (n_splits, n_kv_heads); CTA (s, g) handles cache rows [s*split_len, (s+1)*split_len)
-//          of KV head g for all `G` query heads of that group, so K and V are read once per
-//          group, not once per query head.
-//   block  128 threads; tiles of 64 cache rows, two buffers: the next tile streams in (cp.async)
-//          while this one is used.  Scores: thread t < 64 owns cache row t of the tile and computes
-//          the G dot products in FP32 ascending d, the order of the reference (inference.cu:776-778),
-//          from a 16-byte-chunk XOR-swizzled shared-memory tile (conflict-free row reads).
-//          P.V: thread t owns output dimension t % head_dim.
+//   grid   (n_splits, n_kv_heads, n_seqs); CTA (s, g, b) handles cache rows [s*split_len, (s+1)*split_len)
+//          of KV head g of sequence b for all `G` query heads of that group, so K and V are read once
+//          per group, not once per query head.
+//   block  128 threads = 4 warps; tiles of 64 cache rows in padded shared memory, two buffers: the next
+//          tile streams in (cp.async) while this one is used.  Warp w takes keys 16w..16w+15 of every
+//          tile.  The G query heads are the first G rows of a 16-row mma.sync tile (m16n8k16, FP16 in,
+//          FP32 accumulate): S = q K^T, scores / sqrtf(head_dim) (inference.cu:784), online softmax in
+//          FP32 on the accumulator fragments, O += P V with P split into an FP16 head and an FP16
+//          remainder (two MMAs) so that the probabilities enter the product with ~22 bits, as the
+//          reference's FP32 P does.  The four warps' (max, sum, out) meet in shared memory.
 //   merge  each CTA writes (max, sum, unnormalised out) per query head to scratch; the last
-//          CTA to finish for a KV head (atomic counter) rescales and adds the partials in split
-//          order, normalises and writes FP16 (inference.cu:945).  The counter is left at zero.
+//          CTA to finish for a (sequence, KV head) (atomic counter) rescales and adds the partials in
+//          split order, normalises and writes FP16 (inference.cu:945).  The counter is left at zero.
 #include <mutex>
 
 #include "common.cuh"
+#include "mma_common.cuh"
 
 namespace llmb {
 
@@ -45,186 +49,209 @@ struct AttnParams {
     // consecutive sequences are seq_stride elements apart (0 for a single sequence)
     int n_q;
     size_t seq_stride;
+    unsigned long long *trace;  // optional profiling aid: [CTA][8] global-timer stamps (llmb_attn_decode_trace)
 };
 
 template <int HD, int G>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnParams p) {
-    constexpr int CHUNKS = HD / 8;              // 16-byte chunks per row
-    constexpr int DGROUPS = kAttnThreads / HD;  // thread groups that share one output dim
-    constexpr int HPT = G / DGROUPS;            // query heads per thread in the P.V phase
-    static_assert(G % DGROUPS == 0 && HPT >= 1, "group size must fill the block");
-    extern __shared__ __align__(128) unsigned char attn_smem[];
-    // two buffers of (K tile, V tile); a split of at most one tile needs only the first
-    const int tile_rows = min(kTile, p.split_len);
-    __shared__ __align__(16) float q_s[G * HD];
-    __shared__ __align__(16) float p_s[kTile * G];
-    __shared__ float red_max[4][G];
-    __shared__ float red_sum[4][G];
+    static_assert(G <= 8, "the query heads of a KV head are the first rows of one 16-row MMA tile");
+    constexpr int KP = HD + 8;       // padded tile row: 16-byte aligned, 8 consecutive rows fall in distinct banks
+    constexpr int KS = HD / 16;      // k-steps of q . k
+    constexpr int OT = HD / 8;       // output n-tiles
+    constexpr int CHUNKS = HD / 8;   // 16-byte pieces per cache row
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    typedef __half (*TilePtr)[KP];
+    constexpr size_t kTileBytes = (size_t)kTile * KP * sizeof(__half);
+    __shared__ float wm_s[4][8], wl_s[4][8];  // per warp and query head: running maximum and sum
     __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
     const int split = blockIdx.x, g = blockIdx.y, seq = blockIdx.z;
+    const size_t cta = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    auto stamp = [&](int which) {
+        if (p.trace && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) :: "memory");
+            p.trace[cta * 8 + which] = t;
+        }
+    };
+    stamp(0);
     pdl_launch_dependents();
     pdl_wait();
+    stamp(1);
 
     const int len_total = p.pos[seq] + 1;
-    const __half *q_seq = p.q + (size_t)seq * p.n_q;
+    const int begin = split * p.split_len;
+    // a split that starts past the sequence has nothing to add: the merge below only waits for the splits in use
+    if (begin >= len_total) return;
+    const int end = min(begin + p.split_len, len_total);
+    const __half *q_seq = p.q + (size_t)seq * p.n_q + (size_t)g * G * HD;
     const __half *k_seq = p.k_cache + (size_t)seq * p.seq_stride;
     const __half *v_seq = p.v_cache + (size_t)seq * p.seq_stride;
-    const int gs = seq * p.n_kv_heads + g;  // (sequence, KV head): index of the counter and of the partials
-    const int begin = split * p.split_len;
-    const int end = min(begin + p.split_len, len_total);
     const size_t row_stride = (size_t)p.n_kv_heads * HD;
-    const float inv_den = sqrtf((float)HD);
+    const int gs = seq * p.n_kv_heads + g;  // (sequence, KV head): index of the counter and of the partials
+    const float sqrt_hd = sqrtf((float)HD);
 
-    for (int i = tid; i < G * HD; i += kAttnThreads) q_s[i] = __half2float(q_seq[(size_t)g * G * HD + i]);
-
-    float m_run[G], l_run[G], acc[HPT];
+    // A operand: row r < G of the 16-row tile is query head g * G + r; the other rows are zero
+    uint32_t qf[KS][4];
+    {
+        const bool real = quad_row < G;
+        const __half *qr = q_seq + (size_t)(real ? quad_row : 0) * HD + quad_col;
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m_run[h] = -INFINITY;
-        l_run[h] = 0.0f;
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = real ? *reinterpret_cast<const uint32_t *>(qr + ks * 16) : 0u;
+            qf[ks][2] = real ? *reinterpret_cast<const uint32_t *>(qr + ks * 16 + 8) : 0u;
+            qf[ks][1] = qf[ks][3] = 0u;
+        }
     }
+    float o[OT][4];
 #pragma unroll
-    for (int h = 0; h < HPT; ++h) acc[h] = 0.0f;
-    const int my_d = tid % HD;
-    const int my_h0 = (DGROUPS == 1) ? 0 : (tid / HD) * HPT;
+    for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;  // of row quad_row, over this warp's keys (l: this lane's share)
 
-    // Requests tile i of this split into buffer i & 1 (one cp.async group per tile and thread).
+    // Requests tile i of this split into buffer i & 1; pieces of rows past the split's end are zero-filled.
     auto request_tile = [&](int i) {
-        const int t0 = begin + i * kTile, rows = min(kTile, end - t0);
-        __half *kd = reinterpret_cast<__half *>(attn_smem) + (size_t)(i & 1) * 2 * tile_rows * HD;
-        __half *vd = kd + tile_rows * HD;
-        for (int c = tid; c < rows * CHUNKS; c += kAttnThreads) {
+        TilePtr kd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(i & 1) * 2 * kTileBytes);
+        TilePtr vd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(i & 1) * 2 * kTileBytes + kTileBytes);
+        const int t0 = begin + i * kTile;
+        for (int c = tid; c < kTile * CHUNKS; c += kAttnThreads) {
             const int r = c / CHUNKS, ch = c % CHUNKS;
-            const int sw = ch ^ (r & 7);
-            const size_t goff = (size_t)(t0 + r) * row_stride + (size_t)g * HD + ch * 8;
-            cp_async16(&kd[r * HD + sw * 8], k_seq + goff);
-            cp_async16(&vd[r * HD + ch * 8], v_seq + goff);
+            const bool valid = t0 + r < end;
+            const size_t goff = (size_t)(valid ? t0 + r : begin) * row_stride + (size_t)g * HD + ch * 8;
+            const uint32_t bytes = valid ? 16u : 0u;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&kd[r][ch * 8])), "l"(k_seq + goff), "r"(bytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&vd[r][ch * 8])), "l"(v_seq + goff), "r"(bytes) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int n_tiles = end > begin ? (end - begin + kTile - 1) / kTile : 0;
     if (n_tiles > 0) request_tile(0);
     for (int ti = 0; ti < n_tiles; ++ti) {
-        const int t0 = begin + ti * kTile;
-        const int rows = min(kTile, end - t0);
-        // the next tile streams in while this one is used (its buffer was released by the barrier that ended
-        // the previous iteration)
+        // the next tile streams in while this one is used
         if (ti + 1 < n_tiles) {
             request_tile(ti + 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        __syncthreads();  // every thread's pieces of this tile have landed (also publishes q_s)
-        const __half *k_tile = reinterpret_cast<const __half *>(attn_smem) + (size_t)(ti & 1) * 2 * tile_rows * HD;
-        const __half *v_tile = k_tile + tile_rows * HD;
-
-        // scores for cache row t0 + tid
-        float s[G];
-        const bool active = tid < rows;
+        __syncthreads();  // every thread's pieces of this tile have landed
+        if (ti == 0) stamp(2);
+        TilePtr k_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(ti & 1) * 2 * kTileBytes);
+        TilePtr v_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(ti & 1) * 2 * kTileBytes + kTileBytes);
+        const int key0 = begin + ti * kTile + warp * 16;  // this warp's 16 keys of the tile
+        if (key0 < end) {
+            // S = q K^T for 16 keys: two n-tiles of 8 keys
+            float sc[2][4];
 #pragma unroll
-        for (int h = 0; h < G; ++h) s[h] = 0.0f;
-        if (active) {
+            for (int t = 0; t < 2; ++t) {
+                sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.0f;
+                const __half *kr = &k_s[warp * 16 + t * 8 + quad_row][quad_col];
 #pragma unroll
-            for (int ch = 0; ch < CHUNKS; ++ch) {
-                const uint4 kv = *reinterpret_cast<const uint4 *>(&k_tile[tid * HD + ((ch ^ (tid & 7)) * 8)]);
-                const __half2 *kh = reinterpret_cast<const __half2 *>(&kv);
-                float kf[8];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float2 f = __half22float2(kh[e]);
-                    kf[2 * e] = f.x;
-                    kf[2 * e + 1] = f.y;
-                }
-#pragma unroll
-                for (int h = 0; h < G; ++h) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(&q_s[h * HD + ch * 8]);
-                    const float4 qb = *reinterpret_cast<const float4 *>(&q_s[h * HD + ch * 8 + 4]);
-                    s[h] = fmaf(qa.x, kf[0], s[h]);
-                    s[h] = fmaf(qa.y, kf[1], s[h]);
-                    s[h] = fmaf(qa.z, kf[2], s[h]);
-                    s[h] = fmaf(qa.w, kf[3], s[h]);
-                    s[h] = fmaf(qb.x, kf[4], s[h]);
-                    s[h] = fmaf(qb.y, kf[5], s[h]);
-                    s[h] = fmaf(qb.z, kf[6], s[h]);
-                    s[h] = fmaf(qb.w, kf[7], s[h]);
-                }
+                for (int ks = 0; ks < KS; ++ks)
+                    mma_16816(sc[t], qf[ks], *reinterpret_cast<const uint32_t *>(kr + ks * 16),
+                              *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8));
             }
+            // scale (inference.cu:784), mask keys past the end, row maximum over the 16 keys
+            float tmax = -INFINITY;
 #pragma unroll
-            for (int h = 0; h < G; ++h) s[h] = __fdiv_rn(s[h], inv_den);  // inference.cu:784
-        } else {
+            for (int t = 0; t < 2; ++t) {
+                const int key = key0 + t * 8 + quad_col;
+                sc[t][0] = key < end ? __fdiv_rn(sc[t][0], sqrt_hd) : -INFINITY;
+                sc[t][1] = key + 1 < end ? __fdiv_rn(sc[t][1], sqrt_hd) : -INFINITY;
+                tmax = fmaxf(tmax, fmaxf(sc[t][0], sc[t][1]));
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_new = fmaxf(m_run, tmax);  // finite: key0 < end
+            const float scale = (m_run == -INFINITY) ? 0.0f : expf(m_run - m_new);
+            m_run = m_new;
+            l_run *= scale;
 #pragma unroll
-            for (int h = 0; h < G; ++h) s[h] = -INFINITY;
+            for (int t = 0; t < OT; ++t) {
+                o[t][0] *= scale;
+                o[t][1] *= scale;
+            }
+            // probabilities as the A operand of P V: an FP16 head and an FP16 remainder (two MMAs), so that
+            // they enter the product with ~22 bits, as the reference's FP32 probabilities do
+            uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const float p0 = expf(sc[t][0] - m_new), p1 = expf(sc[t][1] - m_new);  // exp(-inf) = 0 for masked keys
+                l_run += p0 + p1;
+                const __half2 h01 = __floats2half2_rn(p0, p1);
+                const float2 f01 = __half22float2(h01);
+                p_hi[2 * t] = *reinterpret_cast<const uint32_t *>(&h01);
+                p_lo[2 * t] = pack_half2(p0 - f01.x, p1 - f01.y);
+                p_hi[2 * t + 1] = p_lo[2 * t + 1] = 0u;  // rows 8..15 of the tile are not query heads
+            }
+            // O += P V: B fragments of V through ldmatrix.trans (V rows are keys, the MMA wants keys along k)
+#pragma unroll
+            for (int t2 = 0; t2 < OT / 2; ++t2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3, rr = lane & 7;
+                ldmatrix_x4_trans(vb, &v_s[warp * 16 + (mat & 1) * 8 + rr][t2 * 16 + (mat >> 1) * 8]);
+                mma_16816(o[2 * t2], p_hi, vb[0], vb[1]);
+                mma_16816(o[2 * t2], p_lo, vb[0], vb[1]);
+                mma_16816(o[2 * t2 + 1], p_hi, vb[2], vb[3]);
+                mma_16816(o[2 * t2 + 1], p_lo, vb[2], vb[3]);
+            }
         }
-        // tile maximum per head
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float mx = warp_max(s[h]);
-            if (lane == 0) red_max[warp][h] = mx;
-        }
-        __syncthreads();
-        float scale[G];
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float mx = fmaxf(fmaxf(red_max[0][h], red_max[1][h]), fmaxf(red_max[2][h], red_max[3][h]));
-            float m_new = fmaxf(m_run[h], mx);
-            scale[h] = (m_run[h] == -INFINITY) ? 0.0f : expf(m_run[h] - m_new);
-            m_run[h] = m_new;
-            float pv = active ? expf(s[h] - m_new) : 0.0f;
-            l_run[h] = l_run[h] * scale[h] + pv;  // per-thread partial of the softmax denominator
-            if (tid < kTile) p_s[tid * G + h] = pv;   // threads past the tile hold no row
-        }
-        __syncthreads();
-        // P.V for this tile
-#pragma unroll
-        for (int h = 0; h < HPT; ++h) acc[h] *= scale[my_h0 + h];
-        for (int r = 0; r < rows; ++r) {
-            const float vf = __half2float(v_tile[r * HD + my_d]);
-#pragma unroll
-            for (int h = 0; h < HPT; ++h) acc[h] = fmaf(p_s[r * G + my_h0 + h], vf, acc[h]);
-        }
-        __syncthreads();  // this tile's buffer and p_s are free for the tile after next
+        __syncthreads();  // this tile's buffer is free for the tile after next
     }
 
-    // CTA totals: denominators across threads, then publish the partial.
-    __syncthreads();
+    stamp(3);
+    // ---- the four warps' states meet in shared memory (the tile buffers are idle now) ----
+    float *wo_s = reinterpret_cast<float *>(attn_smem);  // [4 warps][G][HD]
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (quad_row < G) {
+        if ((lane & 3) == 0) {
+            wm_s[warp][quad_row] = m_run;
+            wl_s[warp][quad_row] = l_run;
+        }
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        float sm = warp_sum(l_run[h]);
-        if (lane == 0) red_sum[warp][h] = sm;
+        for (int t = 0; t < OT; ++t) {
+            wo_s[((size_t)warp * G + quad_row) * HD + t * 8 + quad_col] = o[t][0];
+            wo_s[((size_t)warp * G + quad_row) * HD + t * 8 + quad_col + 1] = o[t][1];
+        }
     }
     __syncthreads();
+    // CTA partial of (head h, dim d): warps combined in warp order
     const size_t pbase = ((size_t)gs * p.n_splits + split) * G;
-    if (tid < G) {
-        const float l = (red_sum[0][tid] + red_sum[1][tid]) + (red_sum[2][tid] + red_sum[3][tid]);
-        float m = -INFINITY;
+    for (int e = tid; e < G * HD; e += kAttnThreads) {
+        const int h = e / HD, dd = e % HD;
+        const float M = fmaxf(fmaxf(wm_s[0][h], wm_s[1][h]), fmaxf(wm_s[2][h], wm_s[3][h]));
+        float num = 0.0f, den = 0.0f;
 #pragma unroll
-        for (int h = 0; h < G; ++h)
-            if (h == tid) m = m_run[h];
-        p.part_ml[(pbase + tid) * 2] = m;
-        p.part_ml[(pbase + tid) * 2 + 1] = l;
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = (wm_s[w][h] == -INFINITY) ? 0.0f : expf(wm_s[w][h] - M);
+            num = fmaf(wgt, wo_s[((size_t)w * G + h) * HD + dd], num);
+            den = fmaf(wgt, wl_s[w][h], den);
+        }
+        p.part_o[(pbase + h) * HD + dd] = num;
+        if (dd == 0) {
+            p.part_ml[(pbase + h) * 2] = M;
+            p.part_ml[(pbase + h) * 2 + 1] = den;
+        }
     }
-#pragma unroll
-    for (int h = 0; h < HPT; ++h) p.part_o[(pbase + my_h0 + h) * HD + my_d] = acc[h];
     __threadfence();
     __syncthreads();
+    const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
     if (tid == 0) {
         const int prev = atomicAdd(&p.counters[gs], 1);
-        is_last = (prev == p.n_splits - 1);
-        if (is_last) p.counters[gs] = 0;  // every split has arrived; ready for the next launch
+        is_last = (prev == n_used - 1);
+        if (is_last) p.counters[gs] = 0;  // every split in use has arrived; ready for the next launch
     }
     __syncthreads();
+    stamp(4);
     if (!is_last) return;
     __threadfence();
 
     // Merge, in split order.
-    const int n_used = min(p.n_splits, (len_total + p.split_len - 1) / p.split_len);
     const size_t gbase = (size_t)gs * p.n_splits * G;
-#pragma unroll
-    for (int h = 0; h < HPT; ++h) {
-        const int head = my_h0 + h;
+    for (int e = tid; e < G * HD; e += kAttnThreads) {
+        const int head = e / HD, dd = e % HD;
         float M = -INFINITY;
         for (int sidx = 0; sidx < n_used; ++sidx)
             M = fmaxf(M, __ldcg(&p.part_ml[(gbase + (size_t)sidx * G + head) * 2]));
@@ -234,19 +261,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
             const float m = __ldcg(&p.part_ml[pi * 2]);
             const float l = __ldcg(&p.part_ml[pi * 2 + 1]);
             const float wgt = (m == -INFINITY) ? 0.0f : expf(m - M);
-            num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + my_d]), num);
+            num = fmaf(wgt, __ldcg(&p.part_o[pi * HD + dd]), num);
             den = fmaf(wgt, l, den);
         }
-        p.out[(size_t)seq * p.n_q + ((size_t)g * G + head) * HD + my_d] = __float2half_rn(__fdiv_rn(num, den));
+        p.out[(size_t)seq * p.n_q + ((size_t)g * G + head) * HD + dd] = __float2half_rn(__fdiv_rn(num, den));
     }
+    stamp(5);
 }
 
 template <int HD, int G>
 static int launch_attn(const AttnParams &p, int n_seqs, bool pdl, cudaStream_t stream) {
-    // (K tile, V tile) of min(64, split_len) rows, twice if the split has more than one tile
-    const size_t smem = (size_t)(p.split_len > kTile ? 2 : 1) * 2 * (p.split_len < kTile ? p.split_len : kTile) * HD * sizeof(__half);
+    // two buffers of (K tile, V tile), 64 padded rows each
+    const size_t smem = (size_t)4 * kTile * (HD + 8) * sizeof(__half);
     static size_t attr_set[kMaxDevices] = {};  // per instantiation and device
-    LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, (size_t)4 * kTile * HD * sizeof(__half)));
+    LLMB_CUDA_OK(ensure_dynamic_smem(attn_decode_kernel<HD, G>, attr_set, smem));
     LLMB_CUDA_OK(launch_pdl(attn_decode_kernel<HD, G>, dim3(p.n_splits, p.n_kv_heads, n_seqs), dim3(kAttnThreads), smem,
                             stream, pdl, p));
     return LLMB_OK;
@@ -261,6 +289,15 @@ extern "C" size_t llmb_attn_decode_scratch_bytes(int n_q_heads, int n_kv_heads, 
     size_t ml = ((size_t)n_q_heads * n_splits * 2 * 4 + 255) / 256 * 256;
     size_t o = (size_t)n_q_heads * n_splits * head_dim * 4;
     return llmb::attn_counters_bytes(n_kv_heads) + ml + o;
+}
+
+static unsigned long long *g_attn_trace = nullptr;
+
+// Profiling aid: per-CTA global-timer stamps of the next launches (entry, previous kernel complete, first tile
+// landed, tiles done, partial published, merge done) into a device buffer of 8 uint64 per CTA; NULL turns it off.
+extern "C" int llmb_attn_decode_trace(void *d_trace) {
+    g_attn_trace = static_cast<unsigned long long *>(d_trace);
+    return LLMB_OK;
 }
 
 static int attn_decode_impl(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, const int32_t *d_pos,
@@ -290,6 +327,7 @@ static int attn_decode_impl(const uint16_t *d_q, const uint16_t *d_k_cache, cons
     p.split_len = split_len;
     p.n_q = n_q_heads * head_dim;
     p.seq_stride = seq_stride_elems;
+    p.trace = g_attn_trace;
     const int G = n_q_heads / n_kv_heads;
     const bool pdl = use_pdl != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);

@@ -12,6 +12,7 @@
 //   iota           positions pos0 .. pos0 + n - 1 for the embedding / RoPE-angle prologue.
 #include "common.cuh"
 #include "gemv_common.cuh"
+#include "mma_common.cuh"
 
 namespace llmb {
 
@@ -57,24 +58,6 @@ rmsnorm_rows_kernel(const __half *__restrict__ x, const __half *__restrict__ gam
 constexpr int kMmaRows = 64;   // query rows per CTA
 constexpr int kMmaTile = 64;   // cache rows per tile
 constexpr int kMmaThreads = 128;
-
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_u32(smem_row)));
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t *>(&h);
-}
 
 template <int HD>
 __global__ void __launch_bounds__(kMmaThreads)
