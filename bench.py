@@ -297,18 +297,26 @@ def run_ours(args):
 
     # ---- batched decode on this GPU: n_seqs sequences, one token each per step ----------------
     batch = None
-    if single and args.batch > 0:
+    if args.batch > 0 and not args.per_op_kernels:
         B, bp, bsteps = args.batch, args.batch_prompt, args.batch_steps
         cache.batch_init(B)
         prompts = np.array([synth_ids(cfg.vocab, bp, seed=SEED + 1 + b) for b in range(B)], dtype=np.int32)
+        barrier()
         t0 = time.perf_counter()
         cache.batch_prefill(prompts)
         torch.cuda.synchronize()
         bpre_s = time.perf_counter() - t0
+        barrier()
         cache.batch_greedy(3)
+        barrier()
         btoks, bms = cache.batch_greedy(bsteps)
+        if world > 1:
+            bt = torch.tensor([bms, bpre_s], dtype=torch.float64, device="cuda")
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+            bms, bpre_s = bt.tolist()
         rows0 = bp + 3                             # cache rows per sequence before the first timed step
-        bbytes = sum(cfg.weight_bytes_per_token() + B * cfg.kv_bytes_per_position() * (rows0 + i + 1) for i in range(bsteps)) / bsteps
+        bbytes = sum(cfg.weight_bytes_per_token(world) + B * (cfg.kv_bytes_per_position() // world) * (rows0 + i + 1)
+                     for i in range(bsteps)) / bsteps   # per GPU
         bach = bbytes / (bms / bsteps / 1e3) / 1e9
         batch = {"n_seqs": B, "prompt_len": bp, "decode_steps": bsteps, "tok_s": B * bsteps / (bms / 1e3),
                  "ms_per_step": bms / bsteps, "prefill_tok_s": B * (bp - 1) / bpre_s,
@@ -316,7 +324,10 @@ def run_ours(args):
                               "algorithmic_bytes_per_step": bbytes,
                               "scope": "one batched step = weights once + every sequence's KV rows; %d launches per step "
                                        "in a CUDA graph" % (2 + 7 * cfg.n_layers + 2)},
-                 "path": "tcgen05 projections at m = n_seqs rows, split-KV decode attention per sequence, per-row argmax"}
+                 "parallelism": "single GPU" if world == 1 else "tp%d: weight shards streamed once per step on every GPU, all-reduce as "
+                                "peer stores from the projection's epilogue + a local gather kernel" % world,
+                 "path": "tcgen05 projections at m = n_seqs rows (weights as the 128-row operand), tensor-core split-KV decode "
+                         "attention per sequence, per-row argmax"}
 
     times = torch.tensor([ms / 1e3, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:

@@ -237,6 +237,10 @@ int cache_batch_set_split_len(CudaCache *cache, int split_len);
 int cache_batch_prefill(CudaCache *cache, const int *tokens, int n_tokens);
 int cache_batch_step(CudaCache *cache, const int *tokens, uint16_t *h_logits, int *next_tokens);
 int cache_batch_greedy(CudaCache *cache, int n_steps, int *out_tokens, float *ms);
+/* Profiling aid for the batched step: enable = 1 arms per-CTA nanosecond stamps of its small-M projections
+ * (LlmbGemmArgs.trace; projection j of a step, 5 per layer then lm_head, at [j][1024][8] uint64); enable = 0
+ * copies the (5 * n_layers + 1) * 1024 * 8 uint64 to out (optional) and disarms. */
+int cache_debug_rows_trace(CudaCache *cache, int enable, uint64_t *out);
 /* Number of kernels launched (or replayed through graphs) by this cache's stream so far. */
 long long cache_kernel_launches(const CudaCache *cache);
 

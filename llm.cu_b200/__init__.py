@@ -33,7 +33,7 @@ HOST_SYMBOLS = [
     "llama3_to_cuda", "llama3_tensor_shard", "llama3_synth_weights", "llama3_init_cache", "free_cache", "cache_reset",
     "cache_set_options", "cache_use_step_kernel", "cache_set_tp_poll_limit", "cache_tp_handle", "cache_tp_connect", "cache_enable_hidden_dump", "cache_read_hidden", "inference_greedy", "inference_continue", "cache_debug_read", "cache_debug_trace",
     "cache_kernel_launches", "cache_set_prefill", "cache_sample_next_token", "cache_sample_next_token_device", "cache_batch_init", "cache_batch_set_split_len", "cache_batch_prefill",
-    "cache_batch_step", "cache_batch_greedy",
+    "cache_batch_step", "cache_batch_greedy", "cache_debug_rows_trace",
 ]
 
 
@@ -217,6 +217,7 @@ def _declare(l):
     l.cache_batch_prefill.argtypes = [K, vp, i32]
     l.cache_batch_step.argtypes = [K, vp, vp, vp]
     l.cache_batch_greedy.argtypes = [K, i32, vp, C.POINTER(C.c_float)]
+    l.cache_debug_rows_trace.argtypes = [K, i32, vp]
 
 
 lib = None

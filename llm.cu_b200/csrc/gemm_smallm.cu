@@ -71,7 +71,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
     };
     if (threadIdx.x == 0) stamp(0);  // entry
-    pdl_launch_dependents();  // the next kernel may start its own weight stream as soon as an SM has room
+    // The next kernel may start its own weight stream as soon as an SM has room.  After a scattering projection
+    // the next kernel is the gather, which takes no wait of its own and reads the exchange counter and the
+    // residual rows at once: it is let go only after this kernel's wait, when every earlier kernel is complete.
+    const bool scatter = !DUAL && p.epilogue == LLMB_EPI_TP_SCATTER;
+    if (!scatter) pdl_launch_dependents();
     // a wait that gave up earlier (here or in another kernel) leaves the status word set: take no wait at all,
     // but still let the previous kernel finish first so that the order of the chain holds
     if (threadIdx.x == 0) prior_status = *reinterpret_cast<volatile int *>(p.status);
@@ -109,6 +113,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (DUAL) tma_load_2d(st + kWTileBytes, &map_w2, (kt_begin + i) * kBK, n0, &full_bar[i]);
             }
             pdl_wait();  // the activations are the previous kernel's output
+            if (scatter) pdl_launch_dependents();
             stamp(2);    // previous kernel complete
             // a wait that gave up earlier leaves the status word set: do not queue more bounded waits behind it
             bool ok = *reinterpret_cast<volatile int *>(p.status) == 0;

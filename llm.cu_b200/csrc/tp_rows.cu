@@ -7,7 +7,8 @@
 // has already stored every rank's FP32 partial sums, tagged, into every rank's exchange block over NVLink, so
 // the all-reduce is finished by a local kernel:
 //
-//   tp_gather_rows   one CTA per row.  Polls (bounded) the tp_size (value, tag) pairs of each element, adds
+//   tp_gather_rows   one CTA per row; starts while the scattering projection still runs (programmatic
+//                    dependent launch without an upfront wait).  Polls (bounded) the tp_size (value, tag) pairs of each element, adds
 //                    them in rank order (every rank gets the same bits), rounds to FP16 as the projection
 //                    does (:445), adds the residual row in FP32 and rounds (:385-387), writes x, and - if a
 //                    gain vector is given - the RMSNorm of the new row (same partials of four, same binary
@@ -47,7 +48,11 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
     pdl_launch_dependents();
     if (tid == 0) abort_s = 0;
     __syncthreads();
-    pdl_wait();  // the residual rows are an earlier kernel's output; the partial sums carry their own tags
+    // No wait for the previous kernel here: the partial sums carry their own tags, so this kernel may start while
+    // the projection that scatters them is still running and takes each chunk as soon as every rank's pair is there.
+    // The residual row is read only after this rank's own tagged pair of the chunk has been seen: that pair was
+    // stored by the projection's epilogue, which runs after the projection has waited for every earlier kernel -
+    // the one that wrote the residual rows among them.
     const bool ok = *reinterpret_cast<volatile int *>(p.status) == 0;
     const unsigned int tag = *reinterpret_cast<const unsigned int *>(p.exchange + tp_rows_seq_off(p.tp_size, p.d)) +
                              (unsigned int)p.tp_index + 1u;
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
                 }
             }
             float xf[8];
-            unpack8(xr[c], xf);
+            unpack8(__ldcg(xr + c), xf);  // after the tags: see above
             uint4 xn;
             __half2 *o = reinterpret_cast<__half2 *>(&xn);
 #pragma unroll
@@ -103,7 +108,10 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
         part_s[2 * c] = p0;
         part_s[2 * c + 1] = p1;
     }
-    if (!p.gamma) return;
+    if (!p.gamma) {
+        pdl_wait();  // keeps the chain of kernels ordered for the launches that follow
+        return;
+    }
     __syncthreads();  // also orders this CTA's stores of the row before the reads below
     for (int off = p.n_pow2 >> 1; off >= 1; off >>= 1) {
         for (int t = tid; t < off; t += kGatherThreads) part_s[t] += part_s[t + off];
@@ -115,6 +123,7 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
     uint4 *yr = reinterpret_cast<uint4 *>(p.xn + (size_t)row * p.d);
     const uint4 *gr = reinterpret_cast<const uint4 *>(p.gamma);
     for (int c = tid; c < nchunks; c += kGatherThreads) yr[c] = rmsnorm_apply8(xr[c], __ldg(gr + c), rms);
+    pdl_wait();  // keeps the chain of kernels ordered for the launches that follow
 }
 
 struct TpArgmaxParams {

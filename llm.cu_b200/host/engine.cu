@@ -96,6 +96,9 @@ struct Engine {
     int bt_split_len = 256;                             // cache rows per attention CTA (a power of two, 32..512)
     std::vector<int> bt_len;                            // rows in the cache per sequence (host view)
     std::map<int, cudaGraphExec_t> bt_graphs;           // key: attention bucket
+    // profiling aid: per-CTA stamps of every small-M projection of a step (cache_debug_rows_trace)
+    unsigned long long *rows_trace = nullptr;
+    int rows_trace_call = 0;
 };
 
 inline Engine *eng(const CudaCache *c) { return c ? static_cast<Engine *>(c->priv) : nullptr; }
@@ -427,6 +430,8 @@ int prefill_rows(Engine *e, int from, int to, const int *ids, __half *kbase, __h
     return LLMB_OK;
 }
 
+constexpr int kRowsTraceCtas = 1024;  // trace slots per projection (the grid of a small-M projection is smaller)
+
 // One projection of the small-row paths; fills the fields every call shares.
 LlmbGemmArgs small_gemm(Engine *e, const void *a, const void *b, void *c, int m, int n, int k, int epilogue) {
     LlmbGemmArgs g = {};
@@ -437,6 +442,7 @@ LlmbGemmArgs small_gemm(Engine *e, const void *a, const void *b, void *c, int m,
     g.epilogue = epilogue;
     g.workspace = e->pf_ws; g.workspace_bytes = e->pf_ws_bytes;
     g.use_pdl = 1;
+    if (e->rows_trace) g.trace = reinterpret_cast<uint64_t *>(e->rows_trace + (size_t)(e->rows_trace_call++) * kRowsTraceCtas * 8);
     if (epilogue == LLMB_EPI_TP_SCATTER) {
         g.tp_rank = e->tp_rank; g.tp_size = e->tp_size;
         for (int r = 0; r < e->tp_size; ++r) g.tp_peers[r] = e->peers[r];
@@ -577,7 +583,7 @@ void destroy_engine(Engine *e) {
     free_prefill_buffers(e);
     for (auto &kv : e->bt_graphs) cudaGraphExecDestroy(kv.second);
     cudaFree(e->bt_kcache); cudaFree(e->bt_vcache); cudaFree(e->bt_logits); cudaFree(e->bt_pos); cudaFree(e->bt_tok);
-    cudaFree(e->bt_history); cudaFree(e->bt_attn_scratch);
+    cudaFree(e->bt_history); cudaFree(e->bt_attn_scratch); cudaFree(e->rows_trace);
     if (e->h_next) cudaFreeHost(e->h_next);
     for (auto &ev : e->ev)
         if (ev) cudaEventDestroy(ev);
@@ -1074,6 +1080,7 @@ SplitPlan plan_batch_splits(int len, int split_len) {
 }
 
 int enqueue_batch_step(Engine *e, const SplitPlan &sp) {
+    e->rows_trace_call = 0;
     Llama3 *m = e->model;
     const Llama3Config &c = m->config;
     cudaStream_t s = e->stream;
@@ -1193,6 +1200,28 @@ extern "C" int cache_batch_init(CudaCache *cache, int n_seqs) {
     e->bt_seqs = n_seqs;
     e->bt_len.assign((size_t)n_seqs, 0);
     LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    return LLMB_OK;
+}
+
+// Profiling aid: the small-M projections of the following batched steps record per-CTA stamps (see
+// LlmbGemmArgs.trace); projection number j of a step (5 per layer, then lm_head) writes at
+// [j][1024 CTAs][8].  out (host, optional) receives the buffer of (5 * n_layers + 1) * 1024 * 8 uint64.
+// enable = 1 allocates and arms (captured steps are dropped and captured again), 0 reads back and disarms.
+extern "C" int cache_debug_rows_trace(CudaCache *cache, int enable, uint64_t *out) {
+    Engine *e = eng(cache);
+    if (!e) return LLMB_ERR_INVALID;
+    const size_t bytes = (size_t)(5 * e->layers + 1) * kRowsTraceCtas * 8 * sizeof(unsigned long long);
+    LLMB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    for (auto &kv : e->bt_graphs) cudaGraphExecDestroy(kv.second);
+    e->bt_graphs.clear();
+    if (enable) {
+        if (!e->rows_trace) LLMB_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&e->rows_trace), bytes));
+        LLMB_CUDA_OK(cudaMemset(e->rows_trace, 0, bytes));
+    } else if (e->rows_trace) {
+        if (out) LLMB_CUDA_OK(cudaMemcpy(out, e->rows_trace, bytes, cudaMemcpyDeviceToHost));
+        cudaFree(e->rows_trace);
+        e->rows_trace = nullptr;
+    }
     return LLMB_OK;
 }
 

@@ -378,3 +378,55 @@ def test_gemm_small_m_weight_stream_all_epilogues(pkg, oracle, m, use_ws, use_pd
         assert not kgot[untouched].any() and not vgot[untouched].any()
         if use_ws:
             assert not host_u16(ws[:4096].view(torch.int16)).any(), "arrival counters not back to zero"
+
+
+@pytest.mark.parametrize("m,d,k_local", [(32, 512, 256), (7, 4096, 2048)])
+def test_tensor_parallel_row_exchange_two_ranks_on_one_gpu(pkg, oracle, m, d, k_local):
+    """The all-reduce of the row-batched tensor-parallel path with both ranks' kernels run on one GPU in an order
+    in which nothing waits: projection of rank 0 and of rank 1 (LLMB_EPI_TP_SCATTER: each stores its tagged FP32
+    partial sums into BOTH exchange blocks), then the gather kernel of each rank (sum in rank order + residual +
+    RMSNorm).  Two exchanges per step (they alternate between the two receive buffers), two steps (the exchange
+    counter moves on).  Both ranks must end with identical bits, equal to the one-GPU arithmetic."""
+    tp = 2
+    xbytes = pkg.lib.llmb_decode_step_exchange_bytes(tp, d)
+    ex = [torch.zeros(xbytes, dtype=torch.uint8, device="cuda") for _ in range(tp)]
+    peers = (C.c_void_p * 8)(*[e.data_ptr() for e in ex], *([None] * 6))
+    ws = torch.zeros(4096 + 148 * 131072, dtype=torch.uint8, device="cuda")
+    gamma = oracle.synth_fp16(77, 5, d, std=1.0)
+    x_bits = oracle.synth_fp16(77, 6, m * d, std=1.0).reshape(m, d)
+    xs = [dev(x_bits.copy()) for _ in range(tp)]
+    xn = [torch.zeros((m, d), dtype=torch.int16, device="cuda") for _ in range(tp)]
+    d_gamma = dev(gamma)
+    want_x = f16(x_bits).astype(np.float64)
+    for step in range(2):
+        for index in range(2):
+            a_full, b_full = mats(oracle, m, d, tp * k_local, 80 + 2 * step + index)
+            for r in range(tp):   # both projections first: afterwards every partial sum is in place
+                a_r = dev(np.ascontiguousarray(a_full[:, r * k_local:(r + 1) * k_local]))
+                b_r = dev(np.ascontiguousarray(b_full[:, r * k_local:(r + 1) * k_local]))
+                g = pkg.GemmArgs(a=a_r.data_ptr(), b=b_r.data_ptr(), c=None, m=m, n=d, k=k_local, epilogue=pkg.EPI_TP_SCATTER,
+                                 workspace=ws.data_ptr(), workspace_bytes=ws.numel(), use_pdl=1, tp_rank=r, tp_size=tp, tp_index=index)
+                for i in range(tp):
+                    g.tp_peers[i] = peers[i]
+                assert pkg.lib.llmb_gemm_f16(C.byref(g), None) == 0, pkg.lib.llmb_last_error()
+            for r in range(tp):
+                rc = pkg.lib.llmb_tp_gather_rows(ex[r].data_ptr(), tp, index, xs[r].data_ptr(), d_gamma.data_ptr(), xn[r].data_ptr(), m, d,
+                                                 1e-5, 1 << 12, 1, None)
+                assert rc == 0, pkg.lib.llmb_last_error()
+            torch.cuda.synchronize()
+            check_status(pkg)
+            # expected: per-rank FP32 partials added in rank order, rounded to FP16, residual added in FP32, rounded
+            parts = [matmul64(a_full[:, r * k_local:(r + 1) * k_local], b_full[:, r * k_local:(r + 1) * k_local]) for r in range(tp)]
+            acc = parts[0] + parts[1]
+            want_x = acc.astype(np.float16).astype(np.float64) + want_x
+            got0, got1 = host_u16(xs[0]).reshape(m, d), host_u16(xs[1]).reshape(m, d)
+            assert np.array_equal(got0, got1), "the ranks disagree"
+            assert_close_fp16(got0, want_x, what="tp gather x", max_frac=0.1, abs_tol=np.abs(acc) * 2.0 ** -10 + tc_tol(acc, tp * k_local))
+            want_x = f16(got0).astype(np.float64)   # carry the engine's own rounding forward
+            assert np.array_equal(host_u16(xn[0]), host_u16(xn[1]))
+            for row in (0, m - 1):
+                assert np.array_equal(host_u16(xn[0]).reshape(m, d)[row], rmsnorm_ref(got0[row], gamma)), "fused RMSNorm row %d" % row
+        for r in range(tp):
+            assert pkg.lib.llmb_tp_advance(ex[r].data_ptr(), tp, d, 2, 1, None) == 0
+    torch.cuda.synchronize()
+    assert not host_u16(ws[:4096].view(torch.int16)).any(), "arrival counters not back to zero"

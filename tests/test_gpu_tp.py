@@ -143,6 +143,7 @@ def _rank_batch(rank, world, port, cfg_name, n_seqs, n_prompt, n_steps, result_p
     ok, worst = True, 0.0
     for step in range(n_steps + 1):
         feed = None if step == 0 else seqs[:, n_prompt + step - 1]
+        dist.barrier()   # rank 0 spends seconds checking 32 rows of logits: the ranks must enter a step together
         nxt, mine = cache.batch_step(feed)
         parts = [torch.empty(mine.shape, dtype=torch.int32) for _ in range(world)]
         dist.all_gather(parts, torch.from_numpy(mine.astype(np.int32)))
@@ -161,6 +162,7 @@ def _rank_batch(rank, world, port, cfg_name, n_seqs, n_prompt, n_steps, result_p
                     top2 = np.sort(oracle.f16(want))[-2:]
                     ok &= bool(top2[1] - top2[0] <= 2 * diff + 1e-3)
     # device-resident greedy run: the sampled tokens are fed back on every rank alike
+    dist.barrier()   # rank 0 arrives seconds late from its checks; the prefill exchanges data between the ranks
     cache.batch_prefill(seqs[:, :n_prompt])
     dist.barrier()
     greedy, _ = cache.batch_greedy(4)
