@@ -141,7 +141,11 @@ int llmb_attn_decode(const uint16_t *d_q, const uint16_t *d_k_cache, const uint1
                      int n_q_heads, int n_kv_heads, int head_dim, int n_splits, int split_len, uint16_t *d_out,
                      void *d_scratch, int use_pdl, llmb_stream_t stream);
 
-/* Batched decode: one new token for each of n_seqs sequences in one launch (grid z = sequence).   */
+/* Batched decode: one new token for each of n_seqs sequences in one launch.  With 2..256 sequences */
+/* the launch is one wave of CTAs that share the 64-row tiles of all (sequence, KV head) pairs      */
+/* evenly, whatever the mix of lengths (read from pos on the device, so a captured launch stays      */
+/* valid as the sequences grow); a pair is cut into at most n_splits + 1 pieces of at least         */
+/* split_len rows, merged in piece order by the last CTA of the pair to finish.                      */
 /*   q, out   : [n_seqs][n_q_heads * head_dim];  pos : device [n_seqs], position of each new token  */
 /*   k_cache  : [n_seqs][seq_stride_rows][n_kv_heads * head_dim] (this layer), likewise v_cache      */
 /*   n_splits * split_len must cover the longest sequence; scratch as below, counters zero.          */
@@ -206,7 +210,9 @@ int llmb_advance_pos(int32_t *d_pos, int use_pdl, llmb_stream_t stream);
 /* n must be a multiple of 128, k of 64; a, b, c 16-byte aligned; m is free (rows past m are   */
 /* zero-filled on load and never stored).  With m <= 32 (and tile_n 0) the launch is a weight  */
 /* stream: the weight tile is the 128-row MMA operand, the m rows the 32-column one, K is split */
-/* until two CTAs per SM stream weights (workspace as below), bound by HBM like llmb_gemv_f16.  */
+/* until two CTAs per SM stream weights (the slices of a tile are one thread-block cluster and   */
+/* add their partial sums through distributed shared memory: no workspace), bound by HBM like   */
+/* llmb_gemv_f16.                                                                                */
 /* ------------------------------------------------------------------------------------ */
 typedef struct {
     const uint16_t *a;     /* [m][k] FP16 activations */
@@ -222,7 +228,7 @@ typedef struct {
     int pos0;              /* cache row of A's row 0 */
     int max_pos;
     int tile_n;            /* output columns per CTA: 0 = the widest of 128/64/32 that fills the SMs */
-    void *workspace;       /* optional, 16-byte aligned, its first 4096 bytes zero before the first use (the  */
+    void *workspace;       /* m > 32 only. Optional, 16-byte aligned, its first 4096 bytes zero before the first use (the */
     size_t workspace_bytes;/* kernel leaves them zero): lets a launch with few output tiles split K across     */
                            /* CTAs; partial sums are added in slice order.  One launch at a time per workspace; */
                            /* 4096 + SMs * 131072 bytes always suffice.                                        */

@@ -13,7 +13,7 @@ namespace llmb {
 // ---------------------------------------------------------------------------------------
 // Host side: per-device status word that kernels set when a bounded wait gives up.
 // ---------------------------------------------------------------------------------------
-int *device_status_ptr();  // lazily allocated (one int per device, zero-initialised)
+int *device_status_ptr();  // address of the status word (a module variable: one per device, zero at load)
 
 #define LLMB_CUDA_OK(expr)                                                   \
     do {                                                                     \
@@ -172,6 +172,28 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same with the CTAs grouped into thread-block clusters of `cluster` CTAs (a grid dimension must be a
+// multiple of the cluster's); (1, 1, 1) is a plain launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      bool pdl, dim3 cluster, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster.x;
+    attr[1].val.clusterDim.y = cluster.y;
+    attr[1].val.clusterDim.z = cluster.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = cluster.x * cluster.y * cluster.z > 1 ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -12,9 +12,12 @@
 //             (N) operand: D[128 weight rows][32 activation rows] in 32 columns of tensor memory.  A ring stage
 //             is 16 KB of weights + 4 KB of activations (32 KB + 4 KB for the gate/up pair), so nearly all of
 //             the shared memory in flight is weight bytes, and an MMA step costs a quarter of the 128-wide one.
-//   grid      x = 128-row weight tile, y = slice of K.  K is split until about two CTAs per SM exist (each
-//             slice at least 8 K steps); partial accumulators (128 x 32 FP32 = 16 KB) meet in a workspace and
-//             the last CTA of a tile adds them in slice order and runs the epilogue.
+//   grid      x = 128-row weight tile, y = slice of K.  K is split in 2, 4 or 8 until about two CTAs per SM
+//             exist (each slice at least 8 K steps).  The CTAs of one tile form a thread-block cluster: each
+//             leaves its partial accumulators (128 x 32 FP32 = 16 KB) in its own shared memory, and after a
+//             cluster barrier CTA r adds the partials of activation rows r * 32/S .. through distributed
+//             shared memory, in slice order, and runs the epilogue for those rows.  No workspace, no atomic,
+//             no last CTA that reduces alone.
 //   ring      about 100 KB per CTA, so that two CTAs share an SM: two of this launch, or the tail of this
 //             launch and the head of the next one.
 //   overlap   programmatic dependent launch: a CTA releases its dependents at entry and asks for its first
@@ -35,6 +38,35 @@ constexpr uint32_t kXTileBytes = kNX * kBK * 2;           // 4 KB
 constexpr int kSmallMaxStages = 8;
 __host__ __device__ constexpr uint32_t small_stage_bytes(bool dual) { return (dual ? 2 : 1) * kWTileBytes + kXTileBytes; }
 
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Every thread of every CTA of the cluster arrives; returns when all have (a hardware barrier: no spin of ours).
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+// The S slices' partial sums of element (activation row b, weight row nl) of accumulator `acc`, added in slice order.
+// rbase[z] = shared-memory address, as seen from this CTA, of slice z's [accumulator][32][128] FP32 block.
+__device__ __forceinline__ float gather_slices(const uint32_t (&rbase)[8], int n_slices, int acc, int b, int nl) {
+    const uint32_t off = (uint32_t)(((acc * kNX + b) * kBM + nl) * 4);
+    float t[8];
+#pragma unroll
+    for (int z = 0; z < 8; ++z) {
+        t[z] = 0.0f;
+        if (z < n_slices) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[z]) : "r"(rbase[z] + off) : "memory");
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int z = 0; z < 8; ++z)
+        if (z < n_slices) sum += t[z];
+    return sum;
+}
+
 template <bool DUAL>
 __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
@@ -44,13 +76,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ __align__(8) uint64_t empty_bar[kSmallMaxStages];
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_slot;
-    __shared__ int split_last;
     __shared__ int prior_status;
 
     constexpr uint32_t kStageBytes = small_stage_bytes(DUAL);
     constexpr uint32_t kXOff = (DUAL ? 2 : 1) * kWTileBytes;
     constexpr uint32_t kTmemCols = DUAL ? 2 * kNX : kNX;   // 32 is the smallest allocation
-    constexpr int kAcc = DUAL ? 2 * kNX : kNX;
     // kind::f16: D = F32 (bit 4), A = B = F16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kNX >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 
@@ -59,8 +89,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int stages = p.stages;
     const int n0 = blockIdx.x * kBM;
     const int k_tiles = p.K / kBK;
-    const int kt_begin = (int)((long long)blockIdx.y * k_tiles / p.splits);
-    const int kt_end = (int)((long long)(blockIdx.y + 1) * k_tiles / p.splits);
+    const bool clustered = p.splits > 1;  // then the p.splits CTAs of a tile are one cluster along y
+    const int slice = clustered ? (int)cluster_cta_rank() : 0;
+    const int kt_begin = (int)((long long)slice * k_tiles / p.splits);
+    const int kt_end = (int)((long long)(slice + 1) * k_tiles / p.splits);
 
     const int cta = blockIdx.y * gridDim.x + blockIdx.x;
     auto stamp = [&](int which) {
@@ -82,6 +114,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();  // one read for the whole CTA: every thread takes the same way out
     if (prior_status != 0) {
         pdl_wait();
+        if (clustered) {  // the other CTAs of the cluster may still read this one's shared memory: leave with them
+            cluster_sync_all();
+            cluster_sync_all();
+        }
         return;
     }
     if (threadIdx.x == 0) {
@@ -153,131 +189,129 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             stamp(4);  // last MMA issued
             umma_commit(&acc_bar);  // arrives even after a failed wait, so the epilogue never waits forever
         }
-    } else {
-        // ---- epilogue: thread = weight row n0 + lane_group + lane; v[b] = its value for activation row b ----
+    }
+    // ---- epilogue: thread = weight row n0 + lane_group + lane.  The accumulators go to shared memory first (over
+    // the ring), [accumulator][activation row b][weight row]; the rows are then finished four at a time in a loop
+    // that is NOT unrolled over all 32 rows: a CTA runs its epilogue once, so every instruction of it is fetched
+    // cold, and the fully unrolled form (five epilogues x 32 rows) cost 5-19 us of instruction fetch per launch.
+    const int lane_group = (warp & 3) * 32;
+    const int nl = lane_group + lane;
+    const int n = n0 + nl;
+    uint32_t *red_own = reinterpret_cast<uint32_t *>(ring);
+    bool ok = false;
+    if (warp >= 2) {
         const bool got = mbar_wait(&acc_bar, 0, p.status, 313);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (threadIdx.x == 64) stamp(5);  // accumulators complete
         pdl_wait();  // from here on global memory of earlier kernels is read and written
-        const bool ok = got && *reinterpret_cast<volatile int *>(p.status) == 0;
-        const int lane_group = (warp & 3) * 32;
-        const int n = n0 + lane_group + lane;
+        ok = got && *reinterpret_cast<volatile int *>(p.status) == 0;
         const uint32_t taddr = tmem_base + ((uint32_t)lane_group << 16);
-        uint32_t v[32], u[32];
+        // every load of the ring has landed and every MMA has read it (acc_bar): the ring is free
+        uint32_t v[32];
         tmem_ld32(taddr, v);
-        if (DUAL) tmem_ld32(taddr + kNX, u);
-        bool finish = true;
-        if (p.splits > 1) {
-            float *mine = p.ws_part + (((size_t)blockIdx.x * p.splits + blockIdx.y) * kBM + lane_group + lane) * kAcc;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) reinterpret_cast<uint4 *>(mine)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            if (DUAL) {
+        for (int b = 0; b < kNX; ++b) red_own[b * kBM + nl] = v[b];
+        if (DUAL) {
+            tmem_ld32(taddr + kNX, v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    reinterpret_cast<uint4 *>(mine + kNX)[i] = make_uint4(u[4 * i], u[4 * i + 1], u[4 * i + 2], u[4 * i + 3]);
-            }
-            __threadfence();  // this thread's partials are visible device-wide before the arrival is counted
-            named_bar_sync(1, 128);
-            if (threadIdx.x == 64) {
-                const int arrived = atomicAdd(p.ws_count + blockIdx.x, 1);
-                split_last = (arrived == p.splits - 1) ? 1 : 0;
-                if (split_last) p.ws_count[blockIdx.x] = 0;  // ready for the next launch
-                __threadfence();
-            }
-            named_bar_sync(1, 128);
-            if (threadIdx.x == 64) stamp(6);  // partials published, arrival counted
-            finish = split_last != 0;
-            if (finish) {
-                // partial sums in slice order: the result does not depend on which CTA arrived last
-                float fv[32], fu[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) fv[i] = fu[i] = 0.0f;
-                for (int z = 0; z < p.splits; ++z) {
-                    const float *part = p.ws_part + (((size_t)blockIdx.x * p.splits + z) * kBM + lane_group + lane) * kAcc;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 t = __ldcg(reinterpret_cast<const float4 *>(part) + i);
-                        fv[4 * i] += t.x; fv[4 * i + 1] += t.y; fv[4 * i + 2] += t.z; fv[4 * i + 3] += t.w;
-                    }
-                    if (DUAL) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float4 t = __ldcg(reinterpret_cast<const float4 *>(part + kNX) + i);
-                            fu[4 * i] += t.x; fu[4 * i + 1] += t.y; fu[4 * i + 2] += t.z; fu[4 * i + 3] += t.w;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    v[i] = __float_as_uint(fv[i]);
-                    u[i] = __float_as_uint(fu[i]);
-                }
-            }
+            for (int b = 0; b < kNX; ++b) red_own[(kNX + b) * kBM + nl] = v[b];
         }
-        if (finish && ok && n < p.N) {  // the last weight tile may reach past N (its rows are zero-filled by TMA)
-            // Output element (b, n): the 32 lanes of a warp hold 32 consecutive n, so each store of a warp is
-            // one 64-byte run of row b.
+    }
+    // Split K: CTA r of the cluster finishes activation rows r * 32/S ..; without a split a thread only reads back
+    // what it wrote itself, so no barrier is needed.
+    int b_lo = 0, nb = kNX;
+    if (clustered) {
+        cluster_sync_all();  // all slices of the tile are in shared memory
+        nb = kNX / p.splits;
+        b_lo = slice * nb;
+    }
+    if (threadIdx.x == 64) stamp(6);
+    if (warp >= 2 && ok && n < p.N) {  // the last weight tile may reach past N (its rows are zero-filled by TMA)
+        uint32_t rbase[8];
+        const uint32_t red = smem_u32(ring);
+#pragma unroll
+        for (int z = 0; z < 8; ++z) {
+            rbase[z] = red;
+            if (clustered && z < p.splits) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbase[z]) : "r"(red), "r"(z));
+        }
+        const int n_slices = clustered ? p.splits : 1;
+        const int b_hi = min(b_lo + nb, p.M);
+        // Output element (b, n): the 32 lanes of a warp hold 32 consecutive n, so each store of a warp is one
+        // 64-byte run of row b.  Loads of four rows first, then their stores.
+        const int half_dim = p.head_dim >> 1;
+        const bool is_q = n < p.n_q, is_v = n >= p.n_q + p.n_kv;
+        const int local = is_q ? n : (is_v ? n - p.n_q - p.n_kv : n - p.n_q);
+        const int pair = half_dim > 0 ? (local >> 1) % half_dim : 0;
+        const unsigned int tag = p.epilogue == LLMB_EPI_TP_SCATTER ? __ldg(p.tp_seq) + (unsigned int)p.tp_index + 1u : 0u;
+#pragma unroll 1
+        for (int b0 = b_lo; b0 < b_hi; b0 += 4) {
+            float val[4], val2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int b = min(b0 + i, b_hi - 1);
+                val[i] = gather_slices(rbase, n_slices, 0, b, nl);
+                val2[i] = DUAL ? gather_slices(rbase, n_slices, 1, b, nl) : 0.0f;
+            }
             if (!DUAL && p.epilogue == LLMB_EPI_TP_SCATTER) {
                 // tensor parallel: this rank's partial sums go, tagged, to every rank's receive buffer
-                const unsigned int tag = __ldg(p.tp_seq) + (unsigned int)p.tp_index + 1u;
                 const size_t slot0 = tp_rows_slot(p.tp_size, p.N, p.tp_index, p.tp_rank, 0, n);
 #pragma unroll
-                for (int b = 0; b < kNX; ++b) {
-                    if (b < p.M) {
-                        const size_t off = slot0 + (size_t)b * p.N * 8;
+                for (int i = 0; i < 4; ++i) {
+                    if (b0 + i < b_hi) {
+                        const size_t off = slot0 + (size_t)(b0 + i) * p.N * 8;
                         for (int r = 0; r < p.tp_size; ++r)
-                            asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.tp_peer[r] + off), "r"(v[b]), "r"(tag)
+                            asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.tp_peer[r] + off), "r"(__float_as_uint(val[i])),
+                                         "r"(tag)
                                          : "memory");
                     }
                 }
             } else if (DUAL) {
 #pragma unroll
-                for (int b = 0; b < kNX; ++b)
-                    if (b < p.M) p.c[(size_t)b * p.N + n] = __float2half_rn(silu_gemm(__uint_as_float(v[b])) * __uint_as_float(u[b]));
+                for (int i = 0; i < 4; ++i)
+                    if (b0 + i < b_hi) p.c[(size_t)(b0 + i) * p.N + n] = __float2half_rn(silu_gemm(val[i]) * val2[i]);
             } else if (p.epilogue == LLMB_EPI_STORE) {
 #pragma unroll
-                for (int b = 0; b < kNX; ++b)
-                    if (b < p.M) p.c[(size_t)b * p.N + n] = __float2half_rn(__uint_as_float(v[b]));
+                for (int i = 0; i < 4; ++i)
+                    if (b0 + i < b_hi) p.c[(size_t)(b0 + i) * p.N + n] = __float2half_rn(val[i]);
             } else if (p.epilogue == LLMB_EPI_RESIDUAL) {
-                // all residual values first, then the stores: a load after a store to the same array would
-                // have to wait for it, and 32 dependent round trips to L2 cost more than the whole weight stream
-                __half res[kNX];
+                // the residual values of the four rows first, then the stores: a load after a store to the same
+                // array would have to wait for it
+                __half res[4];
 #pragma unroll
-                for (int b = 0; b < kNX; ++b) res[b] = b < p.M ? __ldcg(p.c + (size_t)b * p.N + n) : __half(0);
+                for (int i = 0; i < 4; ++i) res[i] = __ldcg(p.c + (size_t)min(b0 + i, b_hi - 1) * p.N + n);
 #pragma unroll
-                for (int b = 0; b < kNX; ++b)
-                    if (b < p.M)
-                        p.c[(size_t)b * p.N + n] = __float2half_rn(__half2float(__float2half_rn(__uint_as_float(v[b]))) + __half2float(res[b]));
+                for (int i = 0; i < 4; ++i)
+                    if (b0 + i < b_hi)
+                        p.c[(size_t)(b0 + i) * p.N + n] = __float2half_rn(__half2float(__float2half_rn(val[i])) + __half2float(res[i]));
             } else {  // LLMB_EPI_ROPE_KV: the pair (even n, n + 1) sits in neighbouring lanes
-                const int half_dim = p.head_dim >> 1;
-                const bool is_q = n < p.n_q, is_v = n >= p.n_q + p.n_kv;
-                const int local = is_q ? n : (is_v ? n - p.n_q - p.n_kv : n - p.n_q);
-                const int pair = (local >> 1) % half_dim;
-                // angles and cache positions of all rows first (independent loads), then the stores
-                float2 cs[kNX];
-                int pos[kNX];
+                float2 cs[4];
+                int pos[4];
 #pragma unroll
-                for (int b = 0; b < kNX; ++b) {
-                    cs[b] = (b < p.M && !is_v) ? __ldg(p.rope_cs + (size_t)b * half_dim + pair) : make_float2(1.0f, 0.0f);
-                    pos[b] = b < p.M ? (p.row_pos ? __ldg(p.row_pos + b) : p.pos0 + b) : -1;
+                for (int i = 0; i < 4; ++i) {
+                    const int b = min(b0 + i, b_hi - 1);
+                    cs[i] = is_v ? make_float2(1.0f, 0.0f) : __ldg(p.rope_cs + (size_t)b * half_dim + pair);
+                    pos[i] = p.row_pos ? __ldg(p.row_pos + b) : p.pos0 + b;
                 }
 #pragma unroll
-                for (int b = 0; b < kNX; ++b) {
-                    if (b < p.M) {  // uniform across the warp: the shuffle below is executed by all 32 lanes
-                        const float mine = __half2float(__float2half_rn(__uint_as_float(v[b])));
+                for (int i = 0; i < 4; ++i) {
+                    const int b = b0 + i;
+                    // b and b_hi are the same in all lanes, so the shuffle is executed by the whole warp (N is a
+                    // multiple of 32 whenever this epilogue is used: whole heads)
+                    if (b < b_hi) {
+                        const float mine = __half2float(__float2half_rn(val[i]));
                         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
                         __half out;
                         if (is_v) {
-                            out = __float2half_rn(__uint_as_float(v[b]));
+                            out = __float2half_rn(val[i]);
                         } else {
-                            out = __float2half_rn((n & 1) ? __fmaf_rn(cs[b].y, other, __fmul_rn(cs[b].x, mine))
-                                                          : __fmaf_rn(cs[b].x, mine, -__fmul_rn(cs[b].y, other)));
+                            out = __float2half_rn((n & 1) ? __fmaf_rn(cs[i].y, other, __fmul_rn(cs[i].x, mine))
+                                                          : __fmaf_rn(cs[i].x, mine, -__fmul_rn(cs[i].y, other)));
                         }
                         if (is_q) {
                             p.c[(size_t)b * p.n_q + n] = out;
                         } else {
-                            const size_t cache_row = p.row_pos ? (size_t)b * (size_t)p.seq_stride + (size_t)pos[b] : (size_t)pos[b];
-                            if (pos[b] >= 0 && pos[b] < p.max_pos) (is_v ? p.v_cache : p.k_cache)[cache_row * p.n_kv + local] = out;
+                            const size_t cache_row = p.row_pos ? (size_t)b * (size_t)p.seq_stride + (size_t)pos[i] : (size_t)pos[i];
+                            if (pos[i] >= 0 && pos[i] < p.max_pos) (is_v ? p.v_cache : p.k_cache)[cache_row * p.n_kv + local] = out;
                         }
                     }
                 }
@@ -286,6 +320,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (clustered) cluster_sync_all();  // no CTA leaves while another may still read its partial sums
     if (threadIdx.x == 0) stamp(7);  // epilogue done
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -323,21 +358,17 @@ int launch_gemm_smallm(const LlmbGemmArgs *a, cudaStream_t stream) {
         p.tp_seq = reinterpret_cast<const unsigned int *>(p.tp_peer[a->tp_rank] + tp_rows_seq_off(a->tp_size, a->n));
     }
     const int tiles = (a->n + kBM - 1) / kBM, k_tiles = a->k / kBK, sms = sm_count_cached();
-    const int kacc = dual ? 2 * kNX : kNX;
-    // K is split until about two CTAs per SM stream weights, each slice at least 8 K steps long
+    // K is split (2, 4 or 8 slices = the CTAs of one cluster) until about two CTAs per SM stream weights, each
+    // slice at least 8 K steps long.  The gate/up pair moves two weight tiles per CTA: it is split only while
+    // the tiles alone leave half of the SMs without a CTA.
     p.splits = 1;
-    const bool have_ws = a->workspace && a->workspace_bytes > 4096 && (((uintptr_t)a->workspace) & 15) == 0;
-    // (the gate/up pair moves two weight tiles and 32 KB of partials per CTA: it is split only while the tiles
-    // alone leave half of the SMs without a CTA)
-    if (have_ws && tiles <= 1024 && (dual ? tiles * 2 <= sms : tiles < 2 * sms)) {
-        int splits = 2 * sms / tiles;  // never more CTAs than can be resident at once
-        if (splits > k_tiles / 8) splits = k_tiles / 8;
-        if (splits > 16) splits = 16;
-        while (splits > 1 && 4096 + (size_t)tiles * splits * kBM * kacc * sizeof(float) > a->workspace_bytes) --splits;
-        if (splits > 1) p.splits = splits;
+    if (dual ? tiles * 2 <= sms : tiles < 2 * sms) {
+        int want = 2 * sms / tiles;  // never more CTAs than can be resident at once
+        if (want > k_tiles / 8) want = k_tiles / 8;
+        p.splits = want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
     }
-    p.ws_count = static_cast<int *>(a->workspace);
-    p.ws_part = have_ws ? reinterpret_cast<float *>(static_cast<unsigned char *>(a->workspace) + 4096) : nullptr;
+    p.ws_count = nullptr;
+    p.ws_part = nullptr;
     // about 100 KB of ring per CTA: two CTAs (of this launch, or of this and the next one) share an SM
     p.stages = dual ? 3 : 5;  // 108 KB / 100 KB
     if (dual && tiles * p.splits <= sms) p.stages = 5;  // one CTA per SM anyway: a deeper ring (180 KB)
@@ -345,12 +376,12 @@ int launch_gemm_smallm(const LlmbGemmArgs *a, cudaStream_t stream) {
     static size_t attr_set[2][kMaxDevices] = {};  // per instantiation and device
     if (dual) {
         LLMB_CUDA_OK(ensure_dynamic_smem(gemm_smallm_kernel<true>, attr_set[1], smem));
-        LLMB_CUDA_OK(launch_pdl(gemm_smallm_kernel<true>, dim3(tiles, p.splits), dim3(kGemmThreads), smem, stream, a->use_pdl != 0, mw,
-                                mw2, mx, p));
+        LLMB_CUDA_OK(launch_pdl_cluster(gemm_smallm_kernel<true>, dim3(tiles, p.splits), dim3(kGemmThreads), smem, stream, a->use_pdl != 0,
+                                        dim3(1, p.splits, 1), mw, mw2, mx, p));
     } else {
         LLMB_CUDA_OK(ensure_dynamic_smem(gemm_smallm_kernel<false>, attr_set[0], smem));
-        LLMB_CUDA_OK(launch_pdl(gemm_smallm_kernel<false>, dim3(tiles, p.splits), dim3(kGemmThreads), smem, stream, a->use_pdl != 0, mw,
-                                mw2, mx, p));
+        LLMB_CUDA_OK(launch_pdl_cluster(gemm_smallm_kernel<false>, dim3(tiles, p.splits), dim3(kGemmThreads), smem, stream, a->use_pdl != 0,
+                                        dim3(1, p.splits, 1), mw, mw2, mx, p));
     }
     return LLMB_OK;
 }

@@ -19,6 +19,19 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "r"(smem_u32(smem_row)));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+
+// Transposes an 8 x 8 matrix of 16-bit values held across the warp (lane l: row l / 4, columns 2 (l % 4), + 1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&h);

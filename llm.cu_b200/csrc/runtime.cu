@@ -21,6 +21,7 @@ int cuda_fail(cudaError_t e, const char *file, int line) {
 }
 
 static std::mutex g_mu;
+static __device__ __align__(256) int g_status_word[64];  // [0] is the status word; the rest pads the line
 static int *g_status[64] = {};
 static int g_sms[64] = {};
 
@@ -29,10 +30,11 @@ int *device_status_ptr() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_status[dev]) {
-        int *p = nullptr;
-        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
-        if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
-        g_status[dev] = p;
+        // a variable of the module, not an allocation: every device that loads the library has its own copy,
+        // zero when the module is loaded, and looking up its address allocates nothing
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        g_status[dev] = static_cast<int *>(p);
     }
     return g_status[dev];
 }

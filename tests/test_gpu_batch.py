@@ -19,9 +19,13 @@ def _need_gpu():
         pytest.skip("no CUDA device")
 
 
-def test_attn_decode_batch_equals_single_sequence_calls(pkg, oracle):
-    nq, nkv, hd, max_pos, n_seqs, n_splits, split_len = 32, 8, 128, 640, 5, 4, 256
-    lens = [1, 130, 257, 640, 512]
+@pytest.mark.parametrize("lens,n_splits,split_len", [([1, 130, 257, 640, 512], 4, 256), ([640] * 7, 10, 64), ([3, 2, 1], 1, 640),
+                                                     ([64, 65, 128, 129, 1, 640, 600, 77, 300], 3, 256)])
+def test_attn_decode_batch_equals_single_sequence_calls(pkg, oracle, lens, n_splits, split_len):
+    """Several sequences share one wave of CTAs, each taking an equal run of 64-row tiles across the (sequence, KV head)
+    pairs; a pair's pieces therefore fall elsewhere than the fixed splits of the single-sequence call, and the two
+    differ by the order of the FP32 sums: at most one FP16 step.  Two launches of the batch give identical bits."""
+    nq, nkv, hd, max_pos, n_seqs = 32, 8, 128, 640, len(lens)
     q = oracle.synth_fp16(1, 1, n_seqs * nq * hd, std=1.0)
     kc = oracle.synth_fp16(1, 2, n_seqs * max_pos * nkv * hd, std=1.0)
     vc = oracle.synth_fp16(1, 3, n_seqs * max_pos * nkv * hd, std=1.0)
@@ -33,6 +37,11 @@ def test_attn_decode_batch_equals_single_sequence_calls(pkg, oracle):
                                         n_splits, split_len, out.data_ptr(), scratch.data_ptr(), 0, None)
     assert rc == 0, pkg.lib.llmb_last_error()
     got = host_u16(out).reshape(n_seqs, nq * hd)
+    out.zero_()
+    rc = pkg.lib.llmb_attn_decode_batch(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), pos.data_ptr(), n_seqs, max_pos, nq, nkv, hd,
+                                        n_splits, split_len, out.data_ptr(), scratch.data_ptr(), 0, None)
+    assert rc == 0, pkg.lib.llmb_last_error()
+    assert np.array_equal(host_u16(out).reshape(n_seqs, nq * hd), got), "second launch differs (arrival counters, summation order)"
     one = torch.zeros(nq * hd, dtype=torch.int16, device="cuda")
     s1 = torch.zeros(pkg.lib.llmb_attn_decode_scratch_bytes(nq, nkv, hd, n_splits), dtype=torch.uint8, device="cuda")
     for b in range(n_seqs):
@@ -40,7 +49,10 @@ def test_attn_decode_batch_equals_single_sequence_calls(pkg, oracle):
         rc = pkg.lib.llmb_attn_decode(dq.data_ptr() + b * nq * hd * 2, dk.data_ptr() + off, dv.data_ptr() + off,
                                       pos.data_ptr() + 4 * b, nq, nkv, hd, n_splits, split_len, one.data_ptr(), s1.data_ptr(), 0, None)
         assert rc == 0, pkg.lib.llmb_last_error()
-        assert np.array_equal(host_u16(one), got[b]), b   # same kernel, same split order: identical bits
+        a = host_u16(one).view(np.float16).astype(np.float64)
+        g = got[b].view(np.float16).astype(np.float64)
+        assert np.all(np.abs(a - g) <= np.maximum(np.abs(a), 2.0 ** -14) * 2.0 ** -10), (b, np.abs(a - g).max())
+        assert (a != g).mean() < 0.05, (b, (a != g).mean())
 
 
 def test_argmax_rows(pkg, oracle):

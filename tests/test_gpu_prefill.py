@@ -303,9 +303,10 @@ def test_8b_layer_shapes_block_prefill(pkg, oracle, weights_8b_l2):
 
 @pytest.mark.parametrize("m,use_ws,use_pdl", [(1, False, 0), (7, True, 1), (32, True, 1), (20, False, 1)])
 def test_gemm_small_m_weight_stream_all_epilogues(pkg, oracle, m, use_ws, use_pdl):
-    """m <= 32 rows take the weight-streaming kernel (weights as the 128-row MMA operand, K split across CTAs
-    when a workspace is given).  Every epilogue, twice in a row on the same workspace, with and without
-    programmatic dependent launch; the batched-decode form of the cache append (one sequence per row)."""
+    """m <= 32 rows take the weight-streaming kernel (weights as the 128-row MMA operand, K split across the CTAs
+    of a cluster: 8 slices for the store case, 2 for the residual case, 4 for SwiGLU, none for the cache append).
+    Every epilogue, twice in a row, with and without a workspace argument (not used at this m) and programmatic
+    dependent launch; the batched-decode form of the cache append (one sequence per row)."""
     ws = torch.zeros(4096 + 148 * 131072, dtype=torch.uint8, device="cuda") if use_ws else None
     kw = dict(use_pdl=use_pdl, **(dict(workspace=ws, workspace_bytes=ws.numel()) if use_ws else {}))
     for rep in range(2):
