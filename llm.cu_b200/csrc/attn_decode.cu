@@ -157,7 +157,8 @@ __device__ __forceinline__ void attn_decode_segment(const AttnParams &p, const C
     __syncthreads();
     const __half *q_seq = p.q + (size_t)seq * p.n_q + (size_t)g * G * HD;
     const int gs = seq * p.n_kv_heads + g;  // (sequence, KV head): index of the counter and of the partials
-    const float sqrt_hd = sqrtf((float)HD);
+    static_assert(HD == 64 || HD == 128, "div_by_const is checked for sqrtf(64) and sqrtf(128)");
+    const float sqrt_hd = sqrtf((float)HD), rsqrt_hd = __fdiv_rn(1.0f, sqrt_hd);
 
     // The keys are the rows of the MMA tile, the query heads its 8 columns (heads past G are zero columns):
     // S^T[16 keys][8 heads] = K[16 keys][HD] q^T, O^T[HD][8 heads] += V^T[HD][16 keys] P^T[16 keys][8 heads].
@@ -220,10 +221,10 @@ __device__ __forceinline__ void attn_decode_segment(const AttnParams &p, const C
             // keep the score 0, which stays finite through the softmax)
             const bool in_a = key0 + quad_row < end, in_b = key0 + quad_row + 8 < end;
             const bool real0 = quad_col < G, real1 = quad_col + 1 < G;
-            sc[0] = real0 ? (in_a ? __fdiv_rn(sc[0], sqrt_hd) : -INFINITY) : 0.0f;
-            sc[1] = real1 ? (in_a ? __fdiv_rn(sc[1], sqrt_hd) : -INFINITY) : 0.0f;
-            sc[2] = real0 ? (in_b ? __fdiv_rn(sc[2], sqrt_hd) : -INFINITY) : 0.0f;
-            sc[3] = real1 ? (in_b ? __fdiv_rn(sc[3], sqrt_hd) : -INFINITY) : 0.0f;
+            sc[0] = real0 ? (in_a ? div_by_const(sc[0], sqrt_hd, rsqrt_hd) : -INFINITY) : 0.0f;
+            sc[1] = real1 ? (in_a ? div_by_const(sc[1], sqrt_hd, rsqrt_hd) : -INFINITY) : 0.0f;
+            sc[2] = real0 ? (in_b ? div_by_const(sc[2], sqrt_hd, rsqrt_hd) : -INFINITY) : 0.0f;
+            sc[3] = real1 ? (in_b ? div_by_const(sc[3], sqrt_hd, rsqrt_hd) : -INFINITY) : 0.0f;
             float tm0 = fmaxf(sc[0], sc[2]), tm1 = fmaxf(sc[1], sc[3]);
 #pragma unroll
             for (int off = 4; off < 32; off <<= 1) {

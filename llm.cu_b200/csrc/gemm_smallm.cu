@@ -362,7 +362,7 @@ int launch_gemm_smallm(const LlmbGemmArgs *a, cudaStream_t stream) {
     // slice at least 8 K steps long.  The gate/up pair moves two weight tiles per CTA: it is split only while
     // the tiles alone leave half of the SMs without a CTA.
     p.splits = 1;
-    if (dual ? tiles * 2 <= sms : tiles < 2 * sms) {
+    if (tiles < 2 * sms) {
         int want = 2 * sms / tiles;  // never more CTAs than can be resident at once
         if (want > k_tiles / 8) want = k_tiles / 8;
         p.splits = want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;

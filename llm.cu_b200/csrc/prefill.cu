@@ -84,7 +84,8 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
     const int row0 = min(r0, m - 1), row1 = min(r1, m - 1);
     const int qpos0 = pos0 + row0, qpos1 = pos0 + row1;
     const int last_pos = pos0 + min(m0 + kMmaRows, m) - 1;
-    const float sqrt_hd = sqrtf((float)HD);
+    static_assert(HD == 64 || HD == 128, "div_by_const is checked for sqrtf(64) and sqrtf(128)");
+    const float sqrt_hd = sqrtf((float)HD), rsqrt_hd = __fdiv_rn(1.0f, sqrt_hd);
 
     uint32_t qf[KS][4];
     {
@@ -141,23 +142,28 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
         // S = Q K^T: B fragment of n-tile t, k-step ks = K[t * 8 + lane / 4][ks * 16 + 2 (lane % 4) (+ 8)]
         float sc[NT][4];
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.0f;
-            const __half *kr = &k_s[t * 8 + quad_row][quad_col];
+        for (int t = 0; t < NT; ++t) sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.0f;
+        // (one ldmatrix.x4 = the B fragments of two n-tiles of one k-step: K rows are keys, and the MMA wants
+        // the 16 dims of the k-step along k for each key column, which is how a K row lies in memory)
 #pragma unroll
-            for (int ks = 0; ks < KS; ++ks)
-                mma_16816(sc[t], qf[ks], *reinterpret_cast<const uint32_t *>(kr + ks * 16),
-                          *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8));
+        for (int t = 0; t < NT; t += 2) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, &k_s[t * 8 + (lane & 7) + (lane >> 4) * 8][ks * 16 + ((lane >> 3) & 1) * 8]);
+                mma_16816(sc[t], qf[ks], kb[0], kb[1]);
+                mma_16816(sc[t + 1], qf[ks], kb[2], kb[3]);
+            }
         }
         // scale, causal mask, tile maximum per row
         float tmax0 = -INFINITY, tmax1 = -INFINITY;
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const int key = kv0 + t * 8 + quad_col;
-            sc[t][0] = key <= qpos0 ? __fdiv_rn(sc[t][0], sqrt_hd) : -INFINITY;
-            sc[t][1] = key + 1 <= qpos0 ? __fdiv_rn(sc[t][1], sqrt_hd) : -INFINITY;
-            sc[t][2] = key <= qpos1 ? __fdiv_rn(sc[t][2], sqrt_hd) : -INFINITY;
-            sc[t][3] = key + 1 <= qpos1 ? __fdiv_rn(sc[t][3], sqrt_hd) : -INFINITY;
+            sc[t][0] = key <= qpos0 ? div_by_const(sc[t][0], sqrt_hd, rsqrt_hd) : -INFINITY;
+            sc[t][1] = key + 1 <= qpos0 ? div_by_const(sc[t][1], sqrt_hd, rsqrt_hd) : -INFINITY;
+            sc[t][2] = key <= qpos1 ? div_by_const(sc[t][2], sqrt_hd, rsqrt_hd) : -INFINITY;
+            sc[t][3] = key + 1 <= qpos1 ? div_by_const(sc[t][3], sqrt_hd, rsqrt_hd) : -INFINITY;
             tmax0 = fmaxf(tmax0, fmaxf(sc[t][0], sc[t][1]));
             tmax1 = fmaxf(tmax1, fmaxf(sc[t][2], sc[t][3]));
         }
