@@ -326,8 +326,8 @@ def run_ours(args):
                                        "in a CUDA graph" % (2 + 7 * cfg.n_layers + 2)},
                  "parallelism": "single GPU" if world == 1 else "tp%d: weight shards streamed once per step on every GPU, all-reduce as "
                                 "peer stores from the projection's epilogue + a local gather kernel" % world,
-                 "path": "tcgen05 projections at m = n_seqs rows (weights as the 128-row operand), tensor-core split-KV decode "
-                         "attention per sequence, per-row argmax"}
+                 "path": "tcgen05 projections at m = n_seqs rows (weights as the 128-row operand, K slices as a cluster), "
+                         "decode attention as one balanced wave of CTAs over all sequences (TMA boxes, mma.sync), per-row argmax"}
 
     times = torch.tensor([ms / 1e3, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
