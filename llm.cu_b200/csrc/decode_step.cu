@@ -307,8 +307,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     auto grid_arrive = [&]() {
         named_bar_sync(3, kDsThreads);
         if (tid == 0) {
-            if (kTp) __threadfence_system();  // partial sums were stored into the peers' memory
-            else __threadfence();
+            // Device scope also under tensor parallelism: the arrival counter orders this GPU's CTAs only.  What goes
+            // to the peers (the partial sums of o_proj / down_proj) carries its own tag in the same 8-byte store and is
+            // never read on the strength of this counter; a system-scope fence here waited for NVLink in every phase.
+            __threadfence();
             atomicAdd(p.bar, 1ULL);
         }
     };
