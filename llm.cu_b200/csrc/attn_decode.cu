@@ -10,10 +10,11 @@
 //   grid   (n_splits, n_kv_heads, n_seqs); CTA (s, g, b) handles cache rows [s*split_len, (s+1)*split_len)
 //          of KV head g of sequence b for all `G` query heads of that group, so K and V are read once
 //          per group, not once per query head.
-//   block  128 threads = 4 warps; tiles of 64 cache rows in padded shared memory, two buffers: the next
-//          tile streams in while this one is used, as one bulk copy per cache row and thread
-//          (cp.async.bulk, bytes counted on an mbarrier).  Warp w takes keys 16w..16w+15 of every
-//          tile.  Tensor cores through mma.sync (m16n8k16, FP16 in, FP32 accumulate) with the KEYS as the
+//   block  128 threads = 4 warps; tiles of 64 cache rows in shared memory, two buffers: the next tile
+//          streams in while this one is used, bytes counted on an mbarrier - as 64-row boxes through
+//          tensor maps of the K and V cache (cp.async.bulk.tensor.2d, 128-byte swizzle) where the extent
+//          of the cache is known (the batched entry point), else as one bulk copy per cache row and
+//          thread into padded rows (cp.async.bulk).  Warp w takes keys 16w..16w+15 of every tile.  Tensor cores through mma.sync (m16n8k16, FP16 in, FP32 accumulate) with the KEYS as the
 //          16 rows of the tile and the G query heads as its 8 columns: S^T = K q^T, scores /
 //          sqrtf(head_dim) (inference.cu:784), online softmax in FP32 on the accumulator fragments,
 //          O^T += V^T P^T with P split into an FP16 head and an FP16 remainder (two MMAs) so that the
@@ -41,11 +42,6 @@ namespace llmb {
 
 constexpr int kAttnThreads = 128;
 constexpr int kTile = 64;  // cache rows per shared-memory tile; two tiles take turns (one streams in while the other is used)
-
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 struct AttnParams {
     const __half *q;

@@ -527,17 +527,28 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                 const int c = (int)blockIdx.x + (int)gridDim.x * (gtid >> 2);
                 if (c < (p.d >> 3)) {
                     const int e0 = c * 8 + (gtid & 3) * 2;
+                    // The loads of four ranks' pairs go out together and are repeated together until their tags are
+                    // there: one round trip to L2 per four ranks when the data has arrived, not one per rank.
+                    const unsigned char *src = recv + (size_t)e0 * 8;
+                    const size_t rank_stride = (size_t)p.d * 8;
                     float a0 = 0.0f, a1 = 0.0f;
-                    for (int r = 0; r < p.tp_size; ++r) {
-                        const unsigned char *src = recv + ((size_t)r * p.d + (size_t)e0) * 8;
-                        uint4 q;
+                    for (int r0 = 0; r0 < p.tp_size; r0 += 4) {
+                        uint4 q[4];
                         uint32_t spins = 0;
                         for (;;) {
-                            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                                         : "l"(src)
-                                         : "memory");
-                            if ((q.y == tag && q.w == tag) || !ok) break;
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) {
+                                if (r0 + r < p.tp_size)
+                                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                                 : "=r"(q[r].x), "=r"(q[r].y), "=r"(q[r].z), "=r"(q[r].w)
+                                                 : "l"(src + (size_t)(r0 + r) * rank_stride)
+                                                 : "memory");
+                            }
+                            bool all = true;
+#pragma unroll
+                            for (int r = 0; r < 4; ++r)
+                                if (r0 + r < p.tp_size) all = all && q[r].y == tag && q[r].w == tag;
+                            if (all || !ok) break;
                             if ((++spins & 63u) == 0) {  // another wait of this CTA gave up: do not start a new limit
                                 if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
                                 if (spins > p.tag_poll_limit) {
@@ -547,8 +558,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                                 }
                             }
                         }
-                        a0 += __uint_as_float(q.x);
-                        a1 += __uint_as_float(q.z);
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            if (r0 + r < p.tp_size) {  // in rank order: every rank forms the same bits
+                                a0 += __uint_as_float(q[r].x);
+                                a1 += __uint_as_float(q[r].z);
+                            }
+                        }
                     }
                     const float2 xo = __half22float2(*reinterpret_cast<const __half2 *>(g.x_old + e0));
                     const __half2 xn = __halves2half2(__float2half_rn(__half2float(__float2half_rn(a0)) + xo.x),

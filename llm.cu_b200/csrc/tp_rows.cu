@@ -64,20 +64,32 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
             float acc[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-            for (int r = 0; r < p.tp_size; ++r) {
-                const unsigned char *src = p.exchange + tp_rows_slot(p.tp_size, p.d, p.tp_index, r, row, c * 8);
-                uint4 q[4];
+            // The eight elements of a chunk are four 16-byte loads per rank.  Two loads of every rank go out
+            // together and are repeated together until all their tags are there (then the other two): one
+            // round trip to L2 per half when the data has arrived, not one per rank.
+            const unsigned char *src0 = p.exchange + tp_rows_slot(p.tp_size, p.d, p.tp_index, 0, row, c * 8);
+            const size_t rank_stride = tp_rows_slot(p.tp_size, p.d, p.tp_index, 1, row, c * 8) - tp_rows_slot(p.tp_size, p.d, p.tp_index, 0, row, c * 8);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint4 q[8][2];
                 uint32_t spins = 0;
                 for (;;) {
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        if (r < p.tp_size) {
+#pragma unroll
+                            for (int u = 0; u < 2; ++u)
+                                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                             : "=r"(q[r][u].x), "=r"(q[r][u].y), "=r"(q[r][u].z), "=r"(q[r][u].w)
+                                             : "l"(src0 + (size_t)r * rank_stride + 32 * half + 16 * u)
+                                             : "memory");
+                        }
+                    }
                     bool all = true;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
-                                     : "l"(src + 16 * u)
-                                     : "memory");
-                        all = all && q[u].y == tag && q[u].w == tag;
-                    }
+                    for (int r = 0; r < 8; ++r)
+                        if (r < p.tp_size)
+                            all = all && q[r][0].y == tag && q[r][0].w == tag && q[r][1].y == tag && q[r][1].w == tag;
                     if (all || !ok) break;
                     if ((++spins & 63u) == 0) {
                         if (*reinterpret_cast<volatile int *>(&abort_s)) break;
@@ -89,9 +101,14 @@ __global__ void __launch_bounds__(kGatherThreads) tp_gather_rows_kernel(const Ga
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    acc[2 * u] += __uint_as_float(q[u].x);
-                    acc[2 * u + 1] += __uint_as_float(q[u].z);
+                for (int r = 0; r < 8; ++r) {
+                    if (r < p.tp_size) {  // in rank order: every rank forms the same bits
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            acc[4 * half + 2 * u] += __uint_as_float(q[r][u].x);
+                            acc[4 * half + 2 * u + 1] += __uint_as_float(q[r][u].z);
+                        }
+                    }
                 }
             }
             float xf[8];
