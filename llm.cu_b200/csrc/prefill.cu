@@ -10,7 +10,7 @@
 //                  appended, so a chunk that starts at position pos0 > 0 attends to the earlier rows
 //                  as well.
 //   iota           positions pos0 .. pos0 + n - 1 for the embedding / RoPE-angle prologue.
-#include "common.cuh"
+#include "gemm_common.cuh"
 #include "gemv_common.cuh"
 #include "mma_common.cuh"
 
@@ -49,8 +49,8 @@ rmsnorm_rows_kernel(const __half *__restrict__ x, const __half *__restrict__ gam
 
 // ---------------------------------------------------------------------------------------------
 // Block attention on the tensor cores (warp-level mma.sync m16n8k16, FP16 in, FP32 accumulate).
-// CTA = 64 query rows of one head, 4 warps x 16 rows; K/V tiles of 64 cache rows in padded shared
-// memory, double-buffered with cp.async.  Per tile and warp: S = Q K^T (fragments of Q live in registers for the whole kernel),
+// CTA = 64 query rows of one head, 4 warps x 16 rows; K/V tiles of 64 cache rows in shared memory,
+// double-buffered, fetched as swizzled boxes through tensor maps.  Per tile and warp: S = Q K^T (fragments of Q live in registers for the whole kernel),
 // scores / sqrtf(head_dim) and the online softmax in FP32 on the accumulator fragments, then
 // O += P V with P split into an FP16 head and an FP16 remainder (two MMAs), so that the
 // probabilities enter the product with ~22 bits as the reference's FP32 P does, not with 11.
@@ -59,26 +59,33 @@ constexpr int kMmaRows = 64;   // query rows per CTA
 constexpr int kMmaTile = 64;   // cache rows per tile
 constexpr int kMmaThreads = 128;
 
+// Byte offset of 16-byte chunk `chunk` of row `row` in a K (or V) tile as the tensor-map loads leave it: boxes of
+// 64 rows x 128 bytes in the 128-byte swizzle (chunk c of row r sits at chunk c ^ (r & 7)), one box per 64 dims.
+__device__ __forceinline__ uint32_t box_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * (kMmaTile * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
 template <int HD>
-__global__ void __launch_bounds__(kMmaThreads)
-attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__ k_cache,
-                        const __half *__restrict__ v_cache, __half *__restrict__ out, int m, int pos0, int n_q_heads,
-                        int n_kv_heads) {
-    constexpr int KP = HD + 8;     // padded row: 16-byte aligned, and 8 consecutive rows fall in distinct banks
+__global__ void __launch_bounds__(kMmaThreads, 3)
+attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const __half *__restrict__ q, __half *__restrict__ out, int m, int pos0, int n_q_heads, int n_kv_heads,
+                        int *status) {
     constexpr int KS = HD / 16;    // k-steps of Q K^T
     constexpr int NT = kMmaTile / 8;  // score n-tiles per tile
     constexpr int OT = HD / 8;     // output n-tiles
-    // two K/V tile buffers in dynamic shared memory: tile t + 1 streams in (cp.async) while tile t is
-    // multiplied
-    extern __shared__ __align__(16) unsigned char attn_smem[];
-    typedef __half (*TilePtr)[KP];
-    constexpr size_t kTileBytes = (size_t)kMmaTile * KP * sizeof(__half);
+    // two K/V tile buffers in dynamic shared memory: tile t + 1 streams in while tile t is multiplied.  A tile
+    // arrives as 64-row boxes through tensor maps of the K and V cache (rows 0 .. pos0 + m - 1 of this layer):
+    // one instruction per box, where 16-byte cp.async pieces took 32 instructions and their addresses per thread.
+    extern __shared__ __align__(16) unsigned char attn_smem_raw[];
+    unsigned char *attn_smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(attn_smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t tile_bar[2];
+    constexpr size_t kTileBytes = (size_t)kMmaTile * HD * sizeof(__half);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
     const int head = blockIdx.y, kvh = head / (n_q_heads / n_kv_heads);
     const int m0 = blockIdx.x * kMmaRows;
-    const int n_q = n_q_heads * HD, n_kv = n_kv_heads * HD;
+    const int n_q = n_q_heads * HD;
     // this thread's two rows (tail rows repeat the last row and are not stored)
     const int r0 = m0 + warp * 16 + quad_row, r1 = r0 + 8;
     const int row0 = min(r0, m - 1), row1 = min(r1, m - 1);
@@ -104,40 +111,34 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
     for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
     float m_run0 = -INFINITY, m_run1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // l: this thread's share of the row sum
 
-    // Requests tile `t` (cache rows t * 64 ..) into buffer t & 1.  Rows past the last visible key are
-    // never read from the cache: their 16-byte pieces are zero-filled (source size 0).
+    if (tid == 0) {
+        mbar_init(&tile_bar[0], 1);
+        mbar_init(&tile_bar[1], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // Requests tile `t` (cache rows t * 64 ..) into buffer t & 1.  Rows past the last visible key are either
+    // rows of this same block (written by the projection before this kernel: finite, and masked below) or past
+    // the end of the tensor map (zero-filled).
     auto request_tile = [&](int t) {
-        constexpr int kChunks = HD / 8;
-        TilePtr kd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(t & 1) * 2 * kTileBytes);
-        TilePtr vd = reinterpret_cast<TilePtr>(attn_smem + (size_t)(t & 1) * 2 * kTileBytes + kTileBytes);
-        const int kv0 = t * kMmaTile;
-        for (int i = tid; i < kMmaTile * kChunks; i += kMmaThreads) {
-            const int c = i / kChunks, part = i % kChunks;
-            const bool valid = kv0 + c <= last_pos;
-            const size_t off = (size_t)(valid ? kv0 + c : 0) * n_kv + (size_t)kvh * HD + part * 8;
-            const uint32_t bytes = valid ? 16u : 0u;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&kd[c][part * 8])),
-                         "l"(k_cache + off), "r"(bytes)
-                         : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&vd[c][part * 8])),
-                         "l"(v_cache + off), "r"(bytes)
-                         : "memory");
+        if (tid == 0) {
+            unsigned char *kd = attn_smem + (size_t)(t & 1) * 2 * kTileBytes, *vd = kd + kTileBytes;
+            mbar_arrive_expect_tx(&tile_bar[t & 1], (uint32_t)(2 * kTileBytes));
+#pragma unroll
+            for (int b = 0; b < HD / 64; ++b) {
+                tma_load_2d(kd + (size_t)b * kMmaTile * 128, &map_k, kvh * HD + b * 64, t * kMmaTile, &tile_bar[t & 1]);
+                tma_load_2d(vd + (size_t)b * kMmaTile * 128, &map_v, kvh * HD + b * 64, t * kMmaTile, &tile_bar[t & 1]);
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int n_tiles = last_pos / kMmaTile + 1;
     request_tile(0);
     for (int tile = 0; tile < n_tiles; ++tile) {
         const int kv0 = tile * kMmaTile;
-        if (tile + 1 < n_tiles) {
-            request_tile(tile + 1);  // its buffer was released by the barrier that ended the previous iteration
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();  // every thread's pieces of this tile have landed
-        TilePtr k_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(tile & 1) * 2 * kTileBytes);
-        TilePtr v_s = reinterpret_cast<TilePtr>(attn_smem + (size_t)(tile & 1) * 2 * kTileBytes + kTileBytes);
+        // the next tile's buffer was released by the barrier that ended the previous iteration
+        if (tile + 1 < n_tiles) request_tile(tile + 1);
+        mbar_wait_warp(&tile_bar[tile & 1], (tile >> 1) & 1, status, 332, lane);
+        const unsigned char *k_s = attn_smem + (size_t)(tile & 1) * 2 * kTileBytes, *v_s = k_s + kTileBytes;
 
         // S = Q K^T: B fragment of n-tile t, k-step ks = K[t * 8 + lane / 4][ks * 16 + 2 (lane % 4) (+ 8)]
         float sc[NT][4];
@@ -150,7 +151,7 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 uint32_t kb[4];
-                ldmatrix_x4(kb, &k_s[t * 8 + (lane & 7) + (lane >> 4) * 8][ks * 16 + ((lane >> 3) & 1) * 8]);
+                ldmatrix_x4(kb, k_s + box_off(t * 8 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
                 mma_16816(sc[t], qf[ks], kb[0], kb[1]);
                 mma_16816(sc[t + 1], qf[ks], kb[2], kb[3]);
             }
@@ -211,7 +212,7 @@ attn_prefill_mma_kernel(const __half *__restrict__ q, const __half *__restrict__
             for (int t2 = 0; t2 < OT / 2; ++t2) {
                 uint32_t vb[4];
                 const int mat = lane >> 3, rr = lane & 7;
-                ldmatrix_x4_trans(vb, &v_s[j * 16 + (mat & 1) * 8 + rr][t2 * 16 + (mat >> 1) * 8]);
+                ldmatrix_x4_trans(vb, v_s + box_off(j * 16 + (mat & 1) * 8 + rr, t2 * 2 + (mat >> 1)));
                 mma_16816(o[2 * t2], p_hi[j], vb[0], vb[1]);
                 mma_16816(o[2 * t2], p_lo[j], vb[0], vb[1]);
                 mma_16816(o[2 * t2 + 1], p_hi[j], vb[2], vb[3]);
@@ -277,15 +278,26 @@ extern "C" int llmb_attn_prefill(const uint16_t *d_q, const uint16_t *d_k_cache,
         set_last_error("llmb_attn_prefill: head_dim must be 64 or 128");
         return LLMB_ERR_UNSUPPORTED;
     }
-    // two buffers x (K tile + V tile) of 64 padded rows
-    const size_t smem = (size_t)4 * kMmaTile * (head_dim + 8) * sizeof(__half);
+    if ((((uintptr_t)d_k_cache | (uintptr_t)d_v_cache) & 15) || (long long)pos0 + m >= (1ll << 31)) {
+        set_last_error("llmb_attn_prefill: the caches must be 16-byte aligned");
+        return LLMB_ERR_UNSUPPORTED;
+    }
+    // tensor maps of the rows this launch can see: [pos0 + m][n_kv_heads * head_dim], boxes of 64 rows x 64 dims
+    CUtensorMap mk, mv;
+    int rc;
+    if ((rc = make_map(&mk, kc, pos0 + m, n_kv_heads * head_dim, kMmaTile))) return rc;
+    if ((rc = make_map(&mv, vc, pos0 + m, n_kv_heads * head_dim, kMmaTile))) return rc;
+    int *status = device_status_ptr();
+    if (!status) return LLMB_ERR_CUDA;
+    // two buffers x (K tile + V tile) of 64 rows, 1024-byte aligned for the swizzle
+    const size_t smem = (size_t)4 * kMmaTile * head_dim * sizeof(__half) + 1024;
     static size_t attr_set[2][kMaxDevices] = {};  // per instantiation and device
     if (head_dim == 128) {
         LLMB_CUDA_OK(ensure_dynamic_smem(attn_prefill_mma_kernel<128>, attr_set[0], smem));
-        attn_prefill_mma_kernel<128><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
+        attn_prefill_mma_kernel<128><<<grid, kMmaThreads, smem, s>>>(mk, mv, q, o, m, pos0, n_q_heads, n_kv_heads, status);
     } else {
         LLMB_CUDA_OK(ensure_dynamic_smem(attn_prefill_mma_kernel<64>, attr_set[1], smem));
-        attn_prefill_mma_kernel<64><<<grid, kMmaThreads, smem, s>>>(q, kc, vc, o, m, pos0, n_q_heads, n_kv_heads);
+        attn_prefill_mma_kernel<64><<<grid, kMmaThreads, smem, s>>>(mk, mv, q, o, m, pos0, n_q_heads, n_kv_heads, status);
     }
     LLMB_CUDA_OK(cudaGetLastError());
     return LLMB_OK;

@@ -19,12 +19,14 @@ def _need_gpu():
         pytest.skip("no CUDA device")
 
 
-@pytest.mark.parametrize("lens,n_splits,split_len", [([1, 130, 257, 640, 512], 4, 256), ([640] * 7, 10, 64), ([3, 2, 1], 1, 640),
+@pytest.mark.parametrize("lens,n_splits,split_len", [([1, 130, 257, 640, 512], 4, 256), ([640] * 7, 10, 64), ([3, 2, 1], 1, 640), ([577], 3, 200),
                                                      ([64, 65, 128, 129, 1, 640, 600, 77, 300], 3, 256)])
 def test_attn_decode_batch_equals_single_sequence_calls(pkg, oracle, lens, n_splits, split_len):
     """Several sequences share one wave of CTAs, each taking an equal run of 64-row tiles across the (sequence, KV head)
     pairs; a pair's pieces therefore fall elsewhere than the fixed splits of the single-sequence call, and the two
-    differ by the order of the FP32 sums: at most one FP16 step.  Two launches of the batch give identical bits."""
+    differ by the order of the FP32 sums: at most one FP16 step.  Two launches of the batch give identical bits.  A batch
+    of one sequence keeps the fixed splits (here 200 rows, not a multiple of the 64-row tile) and fetches its tiles as
+    boxes through the tensor maps all the same."""
     nq, nkv, hd, max_pos, n_seqs = 32, 8, 128, 640, len(lens)
     q = oracle.synth_fp16(1, 1, n_seqs * nq * hd, std=1.0)
     kc = oracle.synth_fp16(1, 2, n_seqs * max_pos * nkv * hd, std=1.0)
