@@ -576,17 +576,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                                  : "memory");
                 }
             }
-            // (two chunks at a time: their four loads go out together and are repeated together, so a thread with
-            // two chunks pays one round trip to L2 when the row is there, not two)
-            static_assert((kDsJ / 2) % 2 == 0, "chunks of the local row are polled in pairs");
+            // (one chunk after the other: polling both chunks of a thread at once was measured slower, 409 against
+            // 429 tok/s at two GPUs - 75,000 threads poll this row, and twice the bytes per round slow every round)
 #pragma unroll
-            for (int j = 0; j < kDsJ / 2; j += 2) {
-                xh[j] = xh[j + 1] = make_uint4(0, 0, 0, 0);
-                if (have[j]) {  // have[j + 1] implies have[j]
+            for (int j = 0; j < kDsJ / 2; ++j) {
+                xh[j] = make_uint4(0, 0, 0, 0);
+                if (have[j]) {
                     const unsigned char *src = row + (size_t)(gtid + kDsGThreads * j) * 32;  // 4 (FP16 pair, tag) slots
-                    const unsigned char *src2 = row + (size_t)(gtid + kDsGThreads * (j + 1)) * 32;
-                    const bool two = have[j + 1];
-                    uint4 q0, q1, q2 = make_uint4(0, tag, 0, tag), q3 = make_uint4(0, tag, 0, tag);
+                    uint4 q0, q1;
                     uint32_t spins = 0;
                     for (;;) {
                         asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -597,20 +594,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                                      : "=r"(q1.x), "=r"(q1.y), "=r"(q1.z), "=r"(q1.w)
                                      : "l"(src + 16)
                                      : "memory");
-                        if (two) {
-                            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                         : "=r"(q2.x), "=r"(q2.y), "=r"(q2.z), "=r"(q2.w)
-                                         : "l"(src2)
-                                         : "memory");
-                            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                         : "=r"(q3.x), "=r"(q3.y), "=r"(q3.z), "=r"(q3.w)
-                                         : "l"(src2 + 16)
-                                         : "memory");
-                        }
-                        if ((q0.y == tag && q0.w == tag && q1.y == tag && q1.w == tag && q2.y == tag && q2.w == tag && q3.y == tag &&
-                             q3.w == tag) ||
-                            !ok)
-                            break;
+                        if ((q0.y == tag && q0.w == tag && q1.y == tag && q1.w == tag) || !ok) break;
                         if ((++spins & 63u) == 0) {
                             if (*reinterpret_cast<volatile int *>(&sh.abort_flag)) break;
                             if (spins > p.tag_poll_limit) {
@@ -621,7 +605,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                         }
                     }
                     xh[j] = make_uint4(q0.x, q0.z, q1.x, q1.z);
-                    if (two) xh[j + 1] = make_uint4(q2.x, q2.z, q3.x, q3.z);
                 }
             }
 #pragma unroll
