@@ -576,12 +576,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                                  : "memory");
                 }
             }
-            // (one chunk after the other: polling both chunks of a thread at once was measured slower, 409 against
-            // 429 tok/s at two GPUs - 75,000 threads poll this row, and twice the bytes per round slow every round)
+            // Only group 0 polls (one chunk after the other); group 1 takes the row from shared memory afterwards (the
+            // attention tiles, idle in this phase).  148 x 512 threads polling the row took enough of L2's bandwidth
+            // to slow every round of polls: asking for two chunks at once instead of one cost 5 % of the step, and
+            // leaving the polls to one group gained 4 % (430 -> 446 tok/s at two GPUs); a pause between rounds, nothing.
+            uint4 *x_s = reinterpret_cast<uint4 *>(k_tile);  // d_model <= 8192 halves = 16 KB = the K and V tile
 #pragma unroll
             for (int j = 0; j < kDsJ / 2; ++j) {
                 xh[j] = make_uint4(0, 0, 0, 0);
-                if (have[j]) {
+                if (grp == 0 && have[j]) {
                     const unsigned char *src = row + (size_t)(gtid + kDsGThreads * j) * 32;  // 4 (FP16 pair, tag) slots
                     uint4 q0, q1;
                     uint32_t spins = 0;
@@ -605,7 +608,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                         }
                     }
                     xh[j] = make_uint4(q0.x, q0.z, q1.x, q1.z);
+                    x_s[gtid + kDsGThreads * j] = xh[j];
                 }
+            }
+            named_bar_sync(2, kDsConsumers);
+            if (grp == 1) {
+#pragma unroll
+                for (int j = 0; j < kDsJ / 2; ++j)
+                    if (have[j]) xh[j] = x_s[gtid + kDsGThreads * j];
             }
 #pragma unroll
             for (int j = kDsJ / 2; j < kDsJ; ++j) xh[j] = make_uint4(0, 0, 0, 0);
