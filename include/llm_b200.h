@@ -157,8 +157,10 @@ int llmb_attn_decode_batch(const uint16_t *d_q, const uint16_t *d_k_cache, const
                            llmb_stream_t stream);
 
 /* Profiling aid: the following launches of the decode attention record per-CTA nanosecond stamps (entry,    */
-/* previous kernel complete, first tile landed, tiles done, partial published, merge done) into d_trace,       */
-/* 8 uint64 per CTA, CTA index = (seq * n_kv_heads + kv_head) * n_splits + split.  NULL (default) = off.       */
+/* previous kernel complete, first tile landed, tiles done, partial published, merge done - of the CTA's last  */
+/* piece) and the SM cycles its thread 0 spent waiting for tiles and using them, into d_trace: 8 uint64 per    */
+/* CTA, CTA index = (seq * n_kv_heads + kv_head) * n_splits + split for one sequence, the CTA's number in the  */
+/* one-wave grid for several (room for 8 x max(that, resident CTAs) entries).  NULL (default) = off.           */
 int llmb_attn_decode_trace(void *d_trace);
 
 /* The same attention for callers that may not allocate device memory (a host whose own pool  */
