@@ -41,7 +41,8 @@ namespace llmb {
 
 constexpr int kDsWarps = 16;                      // consumer warps
 constexpr int kDsConsumers = kDsWarps * 32;       // 512
-constexpr int kDsThreads = kDsConsumers + 32;     // + the stage finisher
+constexpr int kDsFinishers = 2;                   // stage finisher warps: finisher f takes the stages of consumer group f
+constexpr int kDsThreads = kDsConsumers + 32 * kDsFinishers;
 constexpr int kDsGroups = 2;
 constexpr int kDsGWarps = kDsWarps / kDsGroups;   // 8
 constexpr int kDsGThreads = kDsGWarps * 32;       // 256
@@ -182,7 +183,9 @@ struct DsShared {
     uint64_t full_bar[kDsSlots];   // stage data has landed (bulk-copy byte count)
     uint64_t done_bar[kDsSlots];   // the 8 consumer warps of the stage have left their partials
     float red[kDsSlots][8][kDsGWarps];
-    float res_s[128];  // this CTA's slice of the residual stream for the current projection
+    float res_s[kDsFinishers][128];  // this CTA's slice of the residual stream for the current projection (per finisher)
+    float fin_best_val;              // finisher 1's best logit on its way to finisher 0
+    int fin_best_idx;
     float norm_buf[kDsGroups][512];
     float2 rope_cs[64];
     float q_s[8 * 128];
@@ -240,6 +243,14 @@ __device__ __forceinline__ void issue_next_stage(const DsParams &p, const DsLaye
     bulk_g2s(dst, src, bytes, &full_bar[s], policy);
     if (src2) bulk_g2s(dst + (size_t)c.R * c.row_bytes, src2, bytes, &full_bar[s], policy);
     ++c.it;
+}
+
+// Walks the cursor past one stage without requesting it (the other finisher's).
+template <bool kTp>
+__device__ __forceinline__ void skip_stage(const DsParams &p, const DsLayer *layers, const __half *emb, DsCursor &c, int n_gemv) {
+    const unsigned char *src, *src2;
+    uint32_t bytes;
+    if (cursor_next<kTp>(p, layers, emb, c, n_gemv, src, src2, bytes)) ++c.it;
 }
 
 template <int NR>
@@ -339,8 +350,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         else grid_wait();
     };
 
-    if (warp == kDsWarps) {
-        // =========================== stage finisher ===========================
+    if (warp >= kDsWarps) {
+        // =========================== stage finishers ===========================
+        // Two warps: finisher f takes the stages with it % 2 == f (those of consumer group f) and requests the
+        // stages of the same parity (a slot is refilled with the stage six ahead).  One finisher could not keep up
+        // with the consumers where the stages are already in the ring (QKV, o_proj after the attention): 0.8 us per
+        // stage against 0.5, and the backlog delayed the end of those phases by 2 us.
+        const int fin = warp - kDsWarps;
         const uint64_t policy = policy_evict_first();
         DsCursor cur;
         cur.ph = -1;
@@ -349,14 +365,19 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         cur.w = cur.w2 = nullptr;
         cur.row_bytes = 0;
         cur.n = cur.R = 0;
-        if (lane == 0)
-            for (int k = 0; k < kDsSlots; ++k) issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+        if (lane == 0) {
+            if (fin == 1) skip_stage<kTp>(p, layer_s, emb, cur, n_gemv);
+            for (int k = 0; k < kDsSlots / kDsFinishers; ++k) {
+                issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+                skip_stage<kTp>(p, layer_s, emb, cur, n_gemv);
+            }
+        }
         float best_val = -INFINITY;
         int best_idx = 0x7fffffff;
         uint32_t it = 0;
         // profiling aid: the finisher's own stamps go to slots 4..6 of the phase's trace row
         auto fstamp = [&](int ph, int which) {
-            if (p.trace && lane == 0) {
+            if (p.trace && lane == 0 && fin == 0) {
                 const int tph = ph + (ph + 3) / 4;  // attention phases are interleaved after each QKV
                 p.trace[((size_t)blockIdx.x * (5 * p.n_layers + 2) + tph) * 8 + which] = globaltimer_ns();
             }
@@ -372,16 +393,17 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
             const int res_rows = (g.res && !(kTp && g.scatter >= 0)) ? min((ge - gb) * g.R, g.n - gb * g.R) : 0;
             const bool res_cached = res_rows <= 128;
             if (res_cached) {
-                for (int i = lane; i < res_rows; i += 32) sh.res_s[i] = __half2float(__ldcg(&g.res[gb * g.R + i]));
+                for (int i = lane; i < res_rows; i += 32) sh.res_s[fin][i] = __half2float(__ldcg(&g.res[gb * g.R + i]));
                 __syncwarp();
             }
             for (int rg = gb; rg < ge; ++rg, ++it) {
+                if ((int)(it % kDsFinishers) != fin) continue;
                 const int s = it % kDsSlots;
                 const int row0 = rg * g.R;
                 const int rows = min(g.R, g.n - row0);
                 float res = 0.0f;
                 if (g.res && lane < rows)
-                    res = res_cached ? sh.res_s[row0 - gb * g.R + lane] : __half2float(__ldcg(&g.res[row0 + lane]));
+                    res = res_cached ? sh.res_s[fin][row0 - gb * g.R + lane] : __half2float(__ldcg(&g.res[row0 + lane]));
                 bool got = false;
                 if (ok) {
                     got = mbar_wait_warp(&sh.done_bar[s], (it / kDsSlots) & 1, p.status, 204, lane);
@@ -444,15 +466,29 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
                     }
                 }
                 __syncwarp();
-                // slot s is free (all 8 warps have read it) and its partials are consumed: refill
-                if (lane == 0 && got) issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+                // slot s is free (all 8 warps have read it) and its partials are consumed: refill with the stage six
+                // ahead, and walk the cursor past the other finisher's stage
+                if (lane == 0 && got) {
+                    issue_next_stage<kTp>(p, layer_s, emb, cur, n_gemv, ring, sh.full_bar, policy);
+                    skip_stage<kTp>(p, layer_s, emb, cur, n_gemv);
+                }
             }
             // Stores into the peers' memory are posted over NVLink: the warp that issued them waits for
             // them itself, a fence by another thread after a CTA barrier does not cover them.
             fstamp(ph, 6);
-            if (g.kind == PH_LM && lane == 0) {  // this CTA's best logit travels with the phase's arrival
-                p.amax_val[blockIdx.x] = best_val;
-                p.amax_idx[blockIdx.x] = best_idx;
+            if (g.kind == PH_LM) {  // this CTA's best logit travels with the phase's arrival
+                if (fin == 1 && lane == 0) {
+                    sh.fin_best_val = best_val;
+                    sh.fin_best_idx = best_idx;
+                }
+                named_bar_sync(4, 32 * kDsFinishers);
+                if (fin == 0 && lane == 0) {
+                    const float ov = sh.fin_best_val;
+                    const int oi = sh.fin_best_idx;
+                    if (ov > best_val || (ov == best_val && oi < best_idx)) { best_val = ov; best_idx = oi; }
+                    p.amax_val[blockIdx.x] = best_val;
+                    p.amax_idx[blockIdx.x] = best_idx;
+                }
             }
             grid_arrive();
             if (g.kind == PH_QKV) {  // the consumers' attention phase: keep in step with its barriers
